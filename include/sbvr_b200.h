@@ -1,0 +1,105 @@
+/*
+ * sbvr_b200 — C ABI of the B200 (sm_100a) SBVR quantized-linear library.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream, returns an int
+ * status (0 = ok, negative = error, text via sbvr_strerror) and never throws, exits or
+ * synchronises the device unless its comment says so.  Calls are asynchronous on `stream`.
+ *
+ * Packed weight of a linear layer with N outputs and K inputs (Kp = K rounded up to a
+ * multiple of G), exactly as the reference encoder emits it (reference sbvr/core.py:724-805):
+ *
+ *   bvr        uint32  [Kp/32, N, S]   bit j of bvr[kw][n][s] = plane s of W[n][32*kw + j]
+ *   coeff_idx  uint8 | uint16 [Kp/G, N]   codebook line of group g of row n   (idx_bytes 1 | 2)
+ *   coeff      fp16    [C, S]          codebook ("coeff_cache")
+ * or, with idx_bytes == 0 ("direct" form, no codebook; coeff_idx ignored):
+ *   coeff      fp16    [Kp/G, N, S]    one coefficient line per (group, row)
+ *
+ *   W[n][k] = fp16_rn( sum_s float(line(k/G, n)[s]) * bit_s[n][k] )        (plane order, fp32)
+ *
+ * G (group length along K) is 256 in the reference (sbvr/core.py:222); 128 is also accepted.
+ * fp16 values are passed as `const void*` / `void*` pointing at IEEE binary16 data.
+ */
+#ifndef SBVR_B200_H
+#define SBVR_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define SBVR_API __attribute__((visibility("default")))
+#else
+#define SBVR_API
+#endif
+
+typedef void* sbvr_stream_t;          /* a cudaStream_t */
+typedef struct sbvr_workspace sbvr_workspace_t;
+
+enum {
+    SBVR_OK = 0,
+    SBVR_ERR_BAD_ARG = -1,            /* null pointer, non-positive size, unsupported S / G / idx_bytes */
+    SBVR_ERR_SHAPE = -2,              /* K not a multiple of G, N not a multiple the kernel needs */
+    SBVR_ERR_ALIGN = -3,              /* pointer not aligned as the kernel needs (16 bytes) */
+    SBVR_ERR_CUDA = -4,               /* a CUDA runtime call failed; see sbvr_last_cuda_error */
+    SBVR_ERR_WORKSPACE = -5,          /* workspace missing or too small for this call */
+    SBVR_ERR_TIMEOUT = -6,            /* a bounded device-side wait ran out (read by sbvr_workspace_status) */
+    SBVR_ERR_UNSUPPORTED = -7         /* valid arguments, but no kernel covers the combination */
+};
+
+/* Text for a status code.  Replaces the reference's `throw std::runtime_error(cudaGetErrorString)`
+ * (sbvr/kernels/sbvr_kernel.cu:624-628), which crossed the binding as a Python RuntimeError. */
+SBVR_API const char* sbvr_strerror(int status);
+
+/* cudaError_t of the last failed runtime call made by this library on the calling thread. */
+SBVR_API int sbvr_last_cuda_error(void);
+
+/* Device facts the launch heuristics use.  Replaces `_sbvr_cuda_init` (sbvr/kernels/sbvr_ops.cpp:122-150,
+ * bound at :153), which cached cudaDeviceProp for every device and printed them.  Any out pointer may be NULL. */
+SBVR_API int sbvr_query(int device, int* sm_count, int* smem_per_block_optin, int* l2_bytes, int* cc_major, int* cc_minor);
+
+/* Scratch memory for split-K partial sums, the quantised activation planes and the device status word.
+ * The reference allocates nothing comparable (its kernels keep everything in registers); it does allocate
+ * the output inside the binding (sbvr/kernels/sbvr_ops.cpp:100-101), which here is the caller's job.
+ * `bytes` = 0 picks a default that covers every Llama-3 8B/70B layer shape up to 32 activation rows.
+ * One workspace must not be used by two calls that can overlap on the GPU. */
+SBVR_API int sbvr_workspace_create(sbvr_workspace_t** ws, int device, size_t bytes);
+SBVR_API int sbvr_workspace_destroy(sbvr_workspace_t* ws);
+/* Synchronises `stream`, then reads the device status word: SBVR_OK or SBVR_ERR_TIMEOUT. Resets it. */
+SBVR_API int sbvr_workspace_status(sbvr_workspace_t* ws, sbvr_stream_t stream);
+
+/* Packed weight -> dense fp16 W[N rows, row pitch ldw elements]; columns 0 .. K_out-1 of every row are
+ * written.  K is the padded length the packed tensors cover (multiple of G); K_out <= K is the original
+ * inner length: the reference decoder cuts the zero padding the same way (sbvr/core.py:945-947).
+ * Device counterpart of `sbvr.decode()` (sbvr/core.py:926-949), bit-exact with it. */
+SBVR_API int sbvr_decode_f16(const uint32_t* bvr, const void* coeff_idx, int idx_bytes, const void* coeff, int C,
+                    void* W, int ldw, int N, int K, int K_out, int S, int G, sbvr_stream_t stream);
+
+/* y[M, N] = fp16( x[M, K] . W^T + bias ),  fp16 x (row pitch K), fp32 accumulation, bias NULL = none.
+ * Replaces `_sbvr_row_deq_mm_T(l_w, r_bvr, r_coeff_idx, r_coeff_cache, bias, use_shfl)`
+ * (sbvr/kernels/sbvr_ops.cpp:79-120 -> launch_cuda_sbvr_row_deq_mm_T, sbvr/kernels/sbvr_kernel.cu:876-912),
+ * on the reference's non-transposed weight layout, and the dense `x @ decode().T + bias` the reference's
+ * Llama flow runs (sbvr_utils/utils_llama.py:147, test_sbvr.py:321).  K must be the padded length
+ * (multiple of G).  `ws` may be NULL only for the kernels that need no scratch (see `algo`).
+ *   algo 0 = pick; 1 = SIMT dequantise-and-FMA kernel (any S <= 8, no workspace);
+ *   2 = bit-serial tensor-core kernel (S in {2,3,4}, M <= 4, needs workspace). */
+SBVR_API int sbvr_linear_f16(const void* x, const uint32_t* bvr, const void* coeff_idx, int idx_bytes, const void* coeff,
+                    int C, const void* bias, void* y, int M, int N, int K, int S, int G, int algo,
+                    sbvr_workspace_t* ws, sbvr_stream_t stream);
+
+/* Same product with HOST x and y: copies x in, runs sbvr_linear_f16, copies y out, all on `stream`
+ * (weights stay on the device).  The end-to-end form of the call the reference binding makes with a
+ * CPU activation tensor.  x_host / y_host should be pinned for the copies to be asynchronous. */
+SBVR_API int sbvr_linear_f16_host(const void* x_host, const uint32_t* bvr, const void* coeff_idx, int idx_bytes,
+                         const void* coeff, int C, const void* bias, void* y_host, int M, int N, int K, int S,
+                         int G, int algo, sbvr_workspace_t* ws, sbvr_stream_t stream);
+
+/* Test hook (host only, no GPU): the tile partition of the persistent GEMV grid.  No reference counterpart. */
+SBVR_API int sbvr_debug_b1_partition(int T, int P, int c, int* begin, int* end, int t, int* owner);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SBVR_B200_H */

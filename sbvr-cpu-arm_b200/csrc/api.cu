@@ -1,0 +1,190 @@
+// C ABI of sbvr_b200: argument validation, workspace management and dispatch.  Nothing here
+// computes; see decode.cu, linear_simt.cu, linear_b1.cu.
+#include <mutex>
+
+#include "common.cuh"
+
+namespace sbvr {
+
+thread_local int g_last_cuda_error = 0;
+
+int device_info(int device, DeviceInfo* out) {
+    static std::mutex mu;
+    static DeviceInfo cache[64];
+    static bool have[64] = {false};
+    if (device < 0 || device >= 64) return SBVR_ERR_BAD_ARG;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!have[device]) {
+        DeviceInfo d;
+        SBVR_CUDA_TRY(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, device));
+        SBVR_CUDA_TRY(cudaDeviceGetAttribute(&d.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
+        SBVR_CUDA_TRY(cudaDeviceGetAttribute(&d.l2_bytes, cudaDevAttrL2CacheSize, device));
+        SBVR_CUDA_TRY(cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, device));
+        SBVR_CUDA_TRY(cudaDeviceGetAttribute(&d.cc_minor, cudaDevAttrComputeCapabilityMinor, device));
+        cache[device] = d;
+        have[device] = true;
+    }
+    *out = cache[device];
+    return SBVR_OK;
+}
+
+static int make_packed(PackedW* w, const uint32_t* bvr, const void* coeff_idx, int idx_bytes, const void* coeff, int C,
+                       int N, int K, int S, int G) {
+    if (!bvr || !coeff) return SBVR_ERR_BAD_ARG;
+    if (idx_bytes != 0 && idx_bytes != 1 && idx_bytes != 2) return SBVR_ERR_BAD_ARG;
+    if (idx_bytes != 0 && (!coeff_idx || C < 1 || C > 65536 || (idx_bytes == 1 && C > 256))) return SBVR_ERR_BAD_ARG;
+    if (N < 1 || K < 1 || S < 1 || S > 8) return SBVR_ERR_BAD_ARG;
+    if (G < 32 || G % 32) return SBVR_ERR_BAD_ARG;
+    if (K % G) return SBVR_ERR_SHAPE;
+    if (reinterpret_cast<uintptr_t>(bvr) & 3) return SBVR_ERR_ALIGN;
+    if (reinterpret_cast<uintptr_t>(coeff) & 1) return SBVR_ERR_ALIGN;
+    if (idx_bytes == 2 && (reinterpret_cast<uintptr_t>(coeff_idx) & 1)) return SBVR_ERR_ALIGN;
+    w->bvr = bvr, w->idx = coeff_idx, w->coeff = reinterpret_cast<const __half*>(coeff);
+    w->idx_bytes = idx_bytes, w->C = C, w->N = N, w->K = K, w->S = S, w->G = G;
+    return SBVR_OK;
+}
+
+}  // namespace sbvr
+
+using namespace sbvr;
+
+extern "C" {
+
+const char* sbvr_strerror(int status) {
+    switch (status) {
+        case SBVR_OK: return "ok";
+        case SBVR_ERR_BAD_ARG: return "bad argument (null pointer, non-positive size, or unsupported S / G / idx_bytes / C)";
+        case SBVR_ERR_SHAPE: return "shape not supported (K must be a multiple of G)";
+        case SBVR_ERR_ALIGN: return "pointer alignment too small";
+        case SBVR_ERR_CUDA: return "a CUDA runtime call failed (see sbvr_last_cuda_error)";
+        case SBVR_ERR_WORKSPACE: return "workspace missing or too small";
+        case SBVR_ERR_TIMEOUT: return "a bounded device-side wait ran out";
+        case SBVR_ERR_UNSUPPORTED: return "no kernel covers this combination of arguments";
+        default: return "unknown status";
+    }
+}
+
+int sbvr_last_cuda_error(void) { return g_last_cuda_error; }
+
+int sbvr_query(int device, int* sm_count, int* smem_per_block_optin, int* l2_bytes, int* cc_major, int* cc_minor) {
+    DeviceInfo d;
+    int rc = device_info(device, &d);
+    if (rc) return rc;
+    if (sm_count) *sm_count = d.sm_count;
+    if (smem_per_block_optin) *smem_per_block_optin = d.smem_optin;
+    if (l2_bytes) *l2_bytes = d.l2_bytes;
+    if (cc_major) *cc_major = d.cc_major;
+    if (cc_minor) *cc_minor = d.cc_minor;
+    return SBVR_OK;
+}
+
+int sbvr_workspace_create(sbvr_workspace_t** out, int device, size_t bytes) {
+    if (!out) return SBVR_ERR_BAD_ARG;
+    *out = nullptr;
+    if (bytes == 0) bytes = (size_t)32 << 20;
+    const size_t fixed = 256 + (size_t)SBVR_WS_COUNTERS * 4;
+    if (bytes < fixed + 4096) return SBVR_ERR_BAD_ARG;
+    int prev = 0;
+    SBVR_CUDA_TRY(cudaGetDevice(&prev));
+    SBVR_CUDA_TRY(cudaSetDevice(device));
+    sbvr_workspace* ws = new (std::nothrow) sbvr_workspace();
+    if (!ws) return SBVR_ERR_BAD_ARG;
+    ws->device = device;
+    ws->bytes = bytes;
+    ws->base = nullptr;
+    ws->pinned_status = nullptr;
+    cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&ws->base), bytes);
+    if (e == cudaSuccess) e = cudaMemset(ws->base, 0, fixed);
+    if (e == cudaSuccess) e = cudaMallocHost(&ws->pinned_status, 16);
+    if (e != cudaSuccess) {
+        g_last_cuda_error = (int)e;
+        (void)cudaGetLastError();
+        if (ws->base) cudaFree(ws->base);
+        delete ws;
+        cudaSetDevice(prev);
+        return SBVR_ERR_CUDA;
+    }
+    ws->status = reinterpret_cast<unsigned int*>(ws->base);
+    ws->counters = reinterpret_cast<unsigned int*>(ws->base + 256);
+    ws->dyn = ws->base + fixed;
+    ws->dyn_bytes = bytes - fixed;
+    SBVR_CUDA_TRY(cudaSetDevice(prev));
+    *out = ws;
+    return SBVR_OK;
+}
+
+int sbvr_workspace_destroy(sbvr_workspace_t* ws) {
+    if (!ws) return SBVR_OK;
+    int prev = 0;
+    cudaGetDevice(&prev);
+    cudaSetDevice(ws->device);
+    if (ws->base) cudaFree(ws->base);
+    if (ws->pinned_status) cudaFreeHost(ws->pinned_status);
+    cudaSetDevice(prev);
+    delete ws;
+    return SBVR_OK;
+}
+
+int sbvr_workspace_status(sbvr_workspace_t* ws, sbvr_stream_t stream) {
+    if (!ws) return SBVR_ERR_BAD_ARG;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    unsigned int* h = reinterpret_cast<unsigned int*>(ws->pinned_status);
+    SBVR_CUDA_TRY(cudaMemcpyAsync(h, ws->status, 16, cudaMemcpyDeviceToHost, st));
+    SBVR_CUDA_TRY(cudaStreamSynchronize(st));
+    if (h[0] != 0) {
+        // a kernel gave up: its arrival counters may be half-way; clear everything for the next call
+        SBVR_CUDA_TRY(cudaMemsetAsync(ws->base, 0, 256 + (size_t)SBVR_WS_COUNTERS * 4, st));
+        SBVR_CUDA_TRY(cudaStreamSynchronize(st));
+        return SBVR_ERR_TIMEOUT;
+    }
+    return SBVR_OK;
+}
+
+int sbvr_decode_f16(const uint32_t* bvr, const void* coeff_idx, int idx_bytes, const void* coeff, int C, void* W,
+                    int ldw, int N, int K, int K_out, int S, int G, sbvr_stream_t stream) {
+    PackedW w;
+    int rc = make_packed(&w, bvr, coeff_idx, idx_bytes, coeff, C, N, K, S, G);
+    if (rc) return rc;
+    if (!W || K_out < 1 || K_out > K || ldw < K_out) return SBVR_ERR_BAD_ARG;
+    if (reinterpret_cast<uintptr_t>(W) & 1) return SBVR_ERR_ALIGN;
+    return launch_decode(w, reinterpret_cast<__half*>(W), ldw, K_out, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int sbvr_linear_f16(const void* x, const uint32_t* bvr, const void* coeff_idx, int idx_bytes, const void* coeff, int C,
+                    const void* bias, void* y, int M, int N, int K, int S, int G, int algo, sbvr_workspace_t* ws,
+                    sbvr_stream_t stream) {
+    PackedW w;
+    int rc = make_packed(&w, bvr, coeff_idx, idx_bytes, coeff, C, N, K, S, G);
+    if (rc) return rc;
+    if (!x || !y || M < 1) return SBVR_ERR_BAD_ARG;
+    if ((reinterpret_cast<uintptr_t>(x) & 3) || (reinterpret_cast<uintptr_t>(y) & 1)) return SBVR_ERR_ALIGN;
+    if (algo < 0 || algo > 2) return SBVR_ERR_BAD_ARG;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    const __half* xh = reinterpret_cast<const __half*>(x);
+    const __half* bh = reinterpret_cast<const __half*>(bias);
+    __half* yh = reinterpret_cast<__half*>(y);
+    if (algo == 0) algo = (ws && linear_b1_supported(w, M)) ? 2 : 1;
+    if (algo == 2) return launch_linear_b1(xh, w, bh, yh, M, ws, st);
+    return launch_linear_simt(xh, w, bh, yh, M, st);
+}
+
+int sbvr_linear_f16_host(const void* x_host, const uint32_t* bvr, const void* coeff_idx, int idx_bytes,
+                         const void* coeff, int C, const void* bias, void* y_host, int M, int N, int K, int S, int G,
+                         int algo, sbvr_workspace_t* ws, sbvr_stream_t stream) {
+    if (!ws || !x_host || !y_host || M < 1 || N < 1 || K < 1) return SBVR_ERR_BAD_ARG;
+    // staging buffers for x and y live at the end of the workspace
+    const size_t xb = ((size_t)M * K * 2 + 255) / 256 * 256, yb = ((size_t)M * N * 2 + 255) / 256 * 256;
+    if (xb + yb + ((size_t)8 << 20) > ws->dyn_bytes) return SBVR_ERR_WORKSPACE;
+    char* xd = ws->dyn + ws->dyn_bytes - xb - yb;
+    char* yd = xd + xb;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    SBVR_CUDA_TRY(cudaMemcpyAsync(xd, x_host, (size_t)M * K * 2, cudaMemcpyHostToDevice, st));
+    sbvr_workspace shrunk = *ws;                 // keep the kernels' scratch away from the staging buffers
+    shrunk.dyn_bytes = ws->dyn_bytes - xb - yb;
+    int rc = sbvr_linear_f16(xd, bvr, coeff_idx, idx_bytes, coeff, C, bias, yd, M, N, K, S, G, algo, &shrunk, stream);
+    if (rc) return rc;
+    SBVR_CUDA_TRY(cudaMemcpyAsync(y_host, yd, (size_t)M * N * 2, cudaMemcpyDeviceToHost, st));
+    return SBVR_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,141 @@
+// Shared declarations of the sbvr_b200 library: status codes, the workspace, launch helpers and
+// the few PTX wrappers (mbarrier, bulk asynchronous copy, programmatic dependent launch) the
+// kernels use.  sm_100a only.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/sbvr_b200.h"
+
+namespace sbvr {
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+extern thread_local int g_last_cuda_error;
+
+#define SBVR_CUDA_TRY(expr)                                   \
+    do {                                                      \
+        cudaError_t e__ = (expr);                             \
+        if (e__ != cudaSuccess) {                             \
+            ::sbvr::g_last_cuda_error = (int)e__;             \
+            (void)cudaGetLastError();                         \
+            return SBVR_ERR_CUDA;                             \
+        }                                                     \
+    } while (0)
+
+struct DeviceInfo {
+    int sm_count;
+    int smem_optin;
+    int l2_bytes;
+    int cc_major, cc_minor;
+};
+int device_info(int device, DeviceInfo* out);      // cached per device, read-only after first call
+
+// How a weight's coefficients are addressed.
+struct PackedW {
+    const uint32_t* bvr;     // [K/32, N, S]
+    const void* idx;         // [K/G, N] u8/u16, or unused
+    const __half* coeff;     // [C, S] codebook or [K/G, N, S] direct
+    int idx_bytes;           // 0 direct, 1, 2
+    int C;
+    int N, K, S, G;
+};
+
+}  // namespace sbvr
+
+// The workspace: one device allocation carved into regions.
+struct sbvr_workspace {
+    int device;
+    size_t bytes;
+    char* base;               // device
+    // fixed regions at the start of `base`
+    unsigned int* status;     // [4]   word 0: 0 ok / 1 a bounded wait ran out; word 1: where
+    unsigned int* counters;   // [SBVR_WS_COUNTERS] arrival counters of split-K row tiles, all zero between calls
+    char* dyn;                // rest: activation planes, partial sums
+    size_t dyn_bytes;
+    void* pinned_status;      // host, 16 bytes
+};
+#define SBVR_WS_COUNTERS 8192
+
+namespace sbvr {
+
+int launch_decode(const PackedW& w, __half* W, int ldw, int Kout, cudaStream_t st);
+int launch_linear_simt(const __half* x, const PackedW& w, const __half* bias, __half* y, int M, cudaStream_t st);
+int launch_linear_b1(const __half* x, const PackedW& w, const __half* bias, __half* y, int M,
+                     sbvr_workspace* ws, cudaStream_t st);
+bool linear_b1_supported(const PackedW& w, int M);
+
+// ---------------------------------------------------------------------------------------------
+// device side
+// ---------------------------------------------------------------------------------------------
+#ifdef __CUDACC__
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void fence_mbar_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(2000u)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: gives up after `limit` tries (each try may suspend for about 2 us) and reports it.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, uint32_t limit = 400000u) {
+    for (uint32_t i = 0; i < limit; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+
+// 1-D bulk asynchronous copy global -> shared; both addresses 16-byte aligned, bytes % 16 == 0.
+__device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_u32(dst_smem)),
+                 "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+
+// Programmatic dependent launch: let the next kernel in the stream start its prologue / wait for
+// the previous kernel's memory to be visible.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+// Coefficient line of (group g, row n) as a pointer to S halves.
+__device__ __forceinline__ const __half* coeff_line(const void* idx, int idx_bytes, const __half* coeff, int g, int n,
+                                                    int N, int S) {
+    if (idx_bytes == 0) return coeff + ((size_t)g * N + n) * S;
+    size_t line = (idx_bytes == 1) ? (size_t)((const uint8_t*)idx)[(size_t)g * N + n]
+                                   : (size_t)((const uint16_t*)idx)[(size_t)g * N + n];
+    return coeff + line * S;
+}
+
+#endif  // __CUDACC__
+}  // namespace sbvr

@@ -1,0 +1,10 @@
+"""SBVR on B200: same import surface as the reference package (`sbvr/__init__.py:1`):
+`sbvr.sbvr`, `sbvr._sbvr_serialized`, `sbvr.load`, `sbvr.mm_T`, plus `sbvr.linear` for fp16
+activations.  Importing it loads the CUDA library; there is no CPU implementation."""
+import torch
+
+from .core import sbvr, _sbvr_serialized, load, mm_T, linear  # noqa: F401
+from . import _lib  # noqa: F401
+
+# files written by `save` pickle this class by name (reference sbvr/__init__.py:8)
+torch.serialization.add_safe_globals([_sbvr_serialized])

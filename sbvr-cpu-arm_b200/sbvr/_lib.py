@@ -1,0 +1,103 @@
+"""ctypes binding of libsbvr_b200.so (the C ABI declared in include/sbvr_b200.h).
+
+There is no fallback: if the library is missing, importing this module raises; if a call
+returns a non-zero status, a RuntimeError carrying `sbvr_strerror` is raised, as the reference
+binding raised RuntimeError from `std::runtime_error` (reference sbvr/kernels/sbvr_kernel.cu:624-628).
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+_PKG_ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+LIB_PATH = os.path.join(_PKG_ROOT, "lib", "libsbvr_b200.so")
+
+if not os.path.exists(LIB_PATH):
+    raise ImportError(
+        f"{LIB_PATH} not found: build it with `python sbvr-cpu-arm_b200/build.py` "
+        "(there is no CPU or PyTorch fallback for the SBVR kernels)")
+
+lib = ctypes.CDLL(LIB_PATH)
+
+_vp, _i, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
+_ip = ctypes.POINTER(ctypes.c_int)
+
+lib.sbvr_strerror.argtypes = [_i]
+lib.sbvr_strerror.restype = ctypes.c_char_p
+lib.sbvr_last_cuda_error.argtypes = []
+lib.sbvr_last_cuda_error.restype = _i
+lib.sbvr_query.argtypes = [_i, _ip, _ip, _ip, _ip, _ip]
+lib.sbvr_query.restype = _i
+lib.sbvr_workspace_create.argtypes = [ctypes.POINTER(_vp), _i, _sz]
+lib.sbvr_workspace_create.restype = _i
+lib.sbvr_workspace_destroy.argtypes = [_vp]
+lib.sbvr_workspace_destroy.restype = _i
+lib.sbvr_workspace_status.argtypes = [_vp, _vp]
+lib.sbvr_workspace_status.restype = _i
+lib.sbvr_decode_f16.argtypes = [_vp, _vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _vp]
+lib.sbvr_decode_f16.restype = _i
+lib.sbvr_linear_f16.argtypes = [_vp, _vp, _vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp]
+lib.sbvr_linear_f16.restype = _i
+lib.sbvr_linear_f16_host.argtypes = [_vp, _vp, _vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp]
+lib.sbvr_linear_f16_host.restype = _i
+lib.sbvr_debug_b1_partition.argtypes = [_i, _i, _i, _ip, _ip, _i, _ip]
+lib.sbvr_debug_b1_partition.restype = _i
+
+EXPORTS = ["sbvr_strerror", "sbvr_last_cuda_error", "sbvr_query", "sbvr_workspace_create",
+           "sbvr_workspace_destroy", "sbvr_workspace_status", "sbvr_decode_f16", "sbvr_linear_f16",
+           "sbvr_linear_f16_host", "sbvr_debug_b1_partition"]
+
+
+def strerror(rc: int) -> str:
+    return lib.sbvr_strerror(rc).decode()
+
+
+def check(rc: int, what: str = "sbvr") -> None:
+    if rc != 0:
+        extra = ""
+        if rc == -4:
+            extra = f" (cudaError {lib.sbvr_last_cuda_error()})"
+        raise RuntimeError(f"{what}: {strerror(rc)}{extra}")
+
+
+def query(device: int = 0) -> dict:
+    vals = [ctypes.c_int(0) for _ in range(5)]
+    check(lib.sbvr_query(device, *[ctypes.byref(v) for v in vals]), "sbvr_query")
+    keys = ["sm_count", "smem_per_block_optin", "l2_bytes", "cc_major", "cc_minor"]
+    return {k: v.value for k, v in zip(keys, vals)}
+
+
+class Workspace:
+    """Owns one `sbvr_workspace_t` (device scratch for split-K partial sums and activation planes)."""
+
+    def __init__(self, device: int, nbytes: int = 0):
+        self.handle = _vp()
+        self.device = device
+        check(lib.sbvr_workspace_create(ctypes.byref(self.handle), device, nbytes), "sbvr_workspace_create")
+
+    def status(self, stream: int) -> int:
+        return lib.sbvr_workspace_status(self.handle, _vp(stream))
+
+    def close(self):
+        if self.handle:
+            lib.sbvr_workspace_destroy(self.handle)
+            self.handle = _vp()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+_workspaces: dict = {}
+
+
+def workspace(device: int, stream: int) -> Workspace:
+    """One workspace per (device, stream): calls on one stream are ordered, so they may share scratch."""
+    key = (device, stream)
+    ws = _workspaces.get(key)
+    if ws is None:
+        ws = Workspace(device)
+        _workspaces[key] = ws
+    return ws

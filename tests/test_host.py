@@ -1,0 +1,115 @@
+"""Host-side checks that need no GPU: the C-ABI library loads and exports what the header declares,
+argument validation, the tile partition of the persistent grid, the serialized file format."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol():
+    import sbvr
+    from sbvr import _lib
+    hdr = open(os.path.join(ROOT, "include", "sbvr_b200.h")).read()
+    declared = re.findall(r"SBVR_API\s+[\w\s\*]+?\b(sbvr_\w+)\s*\(", hdr)
+    assert len(declared) >= 10
+    for name in declared:
+        assert hasattr(_lib.lib, name), name
+    assert set(declared) == set(_lib.EXPORTS)
+    assert {"sbvr", "_sbvr_serialized", "load", "mm_T", "linear"} <= set(dir(sbvr))
+
+
+def test_strerror_and_validation_without_gpu():
+    from sbvr import _lib
+    L = _lib.lib
+    assert _lib.strerror(0) == "ok"
+    for rc in range(-7, 0):
+        assert "unknown" not in _lib.strerror(rc)
+    buf = (ctypes.c_uint32 * 64)()
+    p = ctypes.addressof(buf)
+    # null pointers, bad S, bad G, K % G, idx/C mismatch: all rejected before any CUDA call
+    assert L.sbvr_linear_f16(None, p, p, 1, p, 4, None, p, 1, 64, 256, 4, 256, 0, None, None) == -1
+    assert L.sbvr_linear_f16(p, p, p, 1, p, 4, None, p, 1, 64, 256, 9, 256, 0, None, None) == -1
+    assert L.sbvr_linear_f16(p, p, p, 1, p, 4, None, p, 1, 64, 256, 4, 100, 0, None, None) == -1
+    assert L.sbvr_linear_f16(p, p, p, 1, p, 4, None, p, 1, 64, 300, 4, 256, 0, None, None) == -2
+    assert L.sbvr_linear_f16(p, p, p, 1, p, 300, None, p, 1, 64, 256, 4, 256, 0, None, None) == -1
+    assert L.sbvr_linear_f16(p, p, p, 3, p, 4, None, p, 1, 64, 256, 4, 256, 0, None, None) == -1
+    assert L.sbvr_linear_f16(p, p + 1, p, 1, p, 4, None, p, 1, 64, 256, 4, 256, 0, None, None) == -3
+    assert L.sbvr_decode_f16(p, p, 1, p, 4, None, 256, 64, 256, 256, 4, 256, None) == -1
+    assert L.sbvr_decode_f16(p, p, 1, p, 4, p, 100, 64, 256, 256, 4, 256, None) == -1     # ldw < K_out
+    assert L.sbvr_workspace_status(None, None) == -1
+
+
+@pytest.mark.parametrize("T,P", [(1024, 148), (512, 148), (256, 148), (3584, 148), (32064, 148), (5, 148), (148, 148),
+                                 (149, 148), (16, 7), (1000, 3)])
+def test_tile_partition_covers_everything_once(T, P):
+    from sbvr import _lib
+    L = _lib.lib
+    grid = min(T, P)
+    b, e, o = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+    seen = np.zeros(T, np.int32)
+    sizes = []
+    for c in range(grid):
+        L.sbvr_debug_b1_partition(T, grid, c, ctypes.byref(b), ctypes.byref(e), 0, ctypes.byref(o))
+        assert 0 <= b.value <= e.value <= T
+        seen[b.value:e.value] += 1
+        sizes.append(e.value - b.value)
+        for t in {b.value, e.value - 1} if e.value > b.value else set():
+            L.sbvr_debug_b1_partition(T, grid, 0, None, None, t, ctypes.byref(o))
+            assert o.value == c, (t, c, o.value)
+    assert (seen == 1).all()
+    assert max(sizes) - min(sizes) <= 1
+
+
+def test_reference_written_file_loads(golden):
+    """A file saved by the reference's `sbvr.save` unpickles into this package's classes."""
+    import sbvr
+    path = os.path.join(ROOT, "tests", "golden", "ser_enc_s4.pt")
+    w = sbvr.load(path, device=torch.device("cpu"), verbose_level=0)
+    c = golden["enc_s4"]
+    assert w.num_sums == 4 and w.bvr_len == 256
+    assert tuple(w.original_data_shape) == (8, 512)
+    assert np.array_equal(w.bvr.view(torch.int32).numpy().view(np.uint32), c["bvr"])
+    assert np.array_equal(w.coeff_idx.numpy(), c["coeff_idx"])
+    assert np.array_equal(w.coeff_cache.numpy().view(np.uint16), c["coeff_cache"].view(np.uint16))
+
+
+def test_save_load_roundtrip(tmp_path, golden):
+    import sbvr
+    c = golden["syn_u16_s3"]
+    w = sbvr.sbvr.from_packed(torch.from_numpy(c["bvr"].view(np.int32)),
+                              torch.from_numpy(c["coeff_idx"].view(np.int16)).view(torch.uint16),
+                              torch.from_numpy(c["coeff_cache"]), device=torch.device("cpu"))
+    f = str(tmp_path / "w.pt")
+    w.save(f)
+    w2 = sbvr.load(f, device=torch.device("cpu"), verbose_level=0)
+    assert torch.equal(w2.bvr.view(torch.int32), w.bvr.view(torch.int32))
+    assert torch.equal(w2.coeff_idx.view(torch.int16), w.coeff_idx.view(torch.int16))
+    assert torch.equal(w2.coeff_cache, w.coeff_cache)
+    assert w2.num_sums == 3
+
+
+def test_constructor_errors_match_reference():
+    import sbvr
+    with pytest.raises(ValueError):
+        sbvr.sbvr()
+    with pytest.raises(ValueError):
+        sbvr.sbvr(sbvr_serialized=object())
+    with pytest.raises(ValueError):
+        sbvr.sbvr.from_packed(torch.zeros((8, 4, 2), dtype=torch.int32), torch.zeros((1, 4), dtype=torch.uint16),
+                              torch.zeros((4, 2), dtype=torch.float16), device=torch.device("cpu"))
+
+
+def test_no_cpu_fallback():
+    """Without a CUDA device the product path must refuse, not compute somewhere else."""
+    import sbvr
+    w = sbvr.sbvr.from_packed(torch.zeros((8, 64, 2), dtype=torch.int32), torch.zeros((1, 64), dtype=torch.uint8),
+                              torch.zeros((4, 2), dtype=torch.float16), device=torch.device("cpu"))
+    with pytest.raises(RuntimeError):
+        sbvr.linear(torch.zeros((1, 256), dtype=torch.float16), w)
+    with pytest.raises(RuntimeError):
+        w.decode()
