@@ -67,6 +67,17 @@ int launch_linear_simt(const __half* x, const PackedW& w, const __half* bias, __
 int launch_linear_b1(const __half* x, const PackedW& w, const __half* bias, __half* y, int M,
                      sbvr_workspace* ws, cudaStream_t st);
 bool linear_b1_supported(const PackedW& w, int M);
+bool linear_tc_supported(const PackedW& w, int M);
+size_t act_digits_bytes(int M, int K, int G);
+int launch_xdigits(const __half* x, void* buf, int M, int K, int G, cudaStream_t st);
+int launch_linear_tc_digits(const void* buf, const PackedW& w, const __half* bias, __half* y, int M,
+                            sbvr_workspace* ws, cudaStream_t st);
+int launch_linear_tc(const __half* x, const PackedW& w, const __half* bias, __half* y, int M,
+                     sbvr_workspace* ws, cudaStream_t st);
+size_t act_planes_bytes(int M, int K, int G);
+int launch_xquant(const __half* x, void* planes, int M, int K, int G, cudaStream_t st);
+int launch_linear_b1_planes(const void* planes, const PackedW& w, const __half* bias, __half* y, int M,
+                            sbvr_workspace* ws, cudaStream_t st);
 
 // ---------------------------------------------------------------------------------------------
 // device side
@@ -111,6 +122,26 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     return false;
 }
 
+// Bounded wait by elapsed time.  Each try lets the hardware suspend the warp (no issue slots burnt
+// while it sleeps) for up to the hint; the loop gives up after about a second of SM clock.
+__device__ __forceinline__ bool mbar_wait_timed(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    const uint32_t a = smem_u32(bar);
+    long long t0 = 0;
+    for (;;) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+            "selp.b32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(a), "r"(parity), "r"(100000u)
+            : "memory");
+        if (ok) return true;
+        if (t0 == 0) t0 = clock64();
+        else if (clock64() - t0 > 2000000000LL) return false;
+    }
+}
+
 // 1-D bulk asynchronous copy global -> shared; both addresses 16-byte aligned, bytes % 16 == 0.
 __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, uint32_t bytes, uint64_t* bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
@@ -123,6 +154,19 @@ __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, u
 // the previous kernel's memory to be visible.
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// One lane of a converged warp; the compiler keeps the operands of what it guards in uniform registers.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred = 0, laneid = 0;
+    asm volatile(
+        "{\n\t.reg .b32 %%rx;\n\t.reg .pred %%px;\n\t"
+        "elect.sync %%rx|%%px, %2;\n\t"
+        "@%%px mov.s32 %1, 1;\n\t"
+        "mov.s32 %0, %%rx;\n\t}"
+        : "+r"(laneid), "+r"(pred)
+        : "r"(0xFFFFFFFFu));
+    return pred != 0;
+}
 
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");

@@ -442,41 +442,71 @@ static int b1_launch_g(const B1Params& p, int G, int M, int idxb, int grid, int 
     return G == 256 ? b1_launch_m<S, 1>(p, M, idxb, grid, smem, st) : b1_launch_m<S, 2>(p, M, idxb, grid, smem, st);
 }
 
-int launch_linear_b1(const __half* x, const PackedW& w, const __half* bias, __half* y, int M, sbvr_workspace* ws,
-                     cudaStream_t st) {
+static inline size_t round_up_sz(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// Activation planes buffer: [bit-planes: M*KB*512 bytes, padded to 256][steps: M*KB*NSUB floats]
+size_t act_planes_bytes(int M, int K, int G) {
+    const size_t KB = (size_t)K / 256, NSUB = 256 / (size_t)G;
+    return round_up_sz((size_t)M * KB * 512, 256) + round_up_sz((size_t)M * KB * NSUB * 4, 256);
+}
+
+int launch_xquant(const __half* x, void* planes, int M, int K, int G, cudaStream_t st) {
+    if ((G != 256 && G != 128) || K % 256 || M < 1 || M > 65535) return SBVR_ERR_UNSUPPORTED;
+    if (reinterpret_cast<uintptr_t>(planes) & 255) return SBVR_ERR_ALIGN;
+    const int KB = K / 256;
+    uint32_t* xq = reinterpret_cast<uint32_t*>(planes);
+    float* xs = reinterpret_cast<float*>(reinterpret_cast<char*>(planes) + round_up_sz((size_t)M * KB * 512, 256));
+    dim3 qgrid(KB, M);
+    if (G == 256)
+        xquant_kernel<1><<<qgrid, 256, 0, st>>>(x, xq, xs, K, KB);
+    else
+        xquant_kernel<2><<<qgrid, 256, 0, st>>>(x, xq, xs, K, KB);
+    SBVR_CUDA_TRY(cudaGetLastError());
+    return SBVR_OK;
+}
+
+int launch_linear_b1_planes(const void* planes, const PackedW& w, const __half* bias, __half* y, int M,
+                            sbvr_workspace* ws, cudaStream_t st) {
     if (!linear_b1_supported(w, M)) return SBVR_ERR_UNSUPPORTED;
     if (!ws) return SBVR_ERR_WORKSPACE;
+    if (reinterpret_cast<uintptr_t>(planes) & 255) return SBVR_ERR_ALIGN;
     DeviceInfo di;
     int rc = device_info(ws->device, &di);
     if (rc) return rc;
     B1Plan pl;
     rc = b1_plan(w, M, di, &pl);
     if (rc) return rc;
-    const size_t need = round_up((int)pl.xq_bytes, 256) + round_up((int)pl.xs_bytes, 256) + pl.partial_bytes;
-    if (need > ws->dyn_bytes) return SBVR_ERR_WORKSPACE;
+    if (pl.partial_bytes > ws->dyn_bytes) return SBVR_ERR_WORKSPACE;
 
     B1Params p;
     p.bvr = w.bvr, p.idx = w.idx, p.coeff = w.coeff, p.bias = bias, p.y = y;
-    uint32_t* xq = reinterpret_cast<uint32_t*>(ws->dyn);
-    float* xs = reinterpret_cast<float*>(ws->dyn + round_up((int)pl.xq_bytes, 256));
-    p.xq = xq, p.xscale = xs;
-    p.partial = reinterpret_cast<float*>(ws->dyn + round_up((int)pl.xq_bytes, 256) + round_up((int)pl.xs_bytes, 256));
+    p.xq = reinterpret_cast<const uint32_t*>(planes);
+    p.xscale = reinterpret_cast<const float*>(reinterpret_cast<const char*>(planes) +
+                                              round_up_sz((size_t)M * pl.KB * 512, 256));
+    p.partial = reinterpret_cast<float*>(ws->dyn);
     p.counters = ws->counters, p.status = ws->status;
     p.N = w.N, p.K = w.K, p.KB = pl.KB, p.NT = pl.NT, p.T = pl.T, p.C = w.C, p.maxc = pl.maxc, p.D = pl.D;
     p.cache_in_smem = pl.cache_in_smem;
-
-    dim3 qgrid(pl.KB, M);
-    if (w.G == 256)
-        xquant_kernel<1><<<qgrid, 256, 0, st>>>(x, xq, xs, w.K, pl.KB);
-    else
-        xquant_kernel<2><<<qgrid, 256, 0, st>>>(x, xq, xs, w.K, pl.KB);
-    SBVR_CUDA_TRY(cudaGetLastError());
-
     switch (w.S) {
         case 2: return b1_launch_g<2>(p, w.G, M, w.idx_bytes, pl.grid, pl.smem, st);
         case 3: return b1_launch_g<3>(p, w.G, M, w.idx_bytes, pl.grid, pl.smem, st);
         default: return b1_launch_g<4>(p, w.G, M, w.idx_bytes, pl.grid, pl.smem, st);
     }
+}
+
+// x -> planes (at the end of the workspace) -> product
+int launch_linear_b1(const __half* x, const PackedW& w, const __half* bias, __half* y, int M, sbvr_workspace* ws,
+                     cudaStream_t st) {
+    if (!linear_b1_supported(w, M)) return SBVR_ERR_UNSUPPORTED;
+    if (!ws) return SBVR_ERR_WORKSPACE;
+    const size_t pb = act_planes_bytes(M, w.K, w.G);
+    if (pb + ((size_t)1 << 20) > ws->dyn_bytes) return SBVR_ERR_WORKSPACE;
+    char* planes = ws->dyn + ((ws->dyn_bytes - pb) & ~(size_t)255);
+    int rc = launch_xquant(x, planes, M, w.K, w.G, st);
+    if (rc) return rc;
+    sbvr_workspace shrunk = *ws;
+    shrunk.dyn_bytes = (size_t)(planes - ws->dyn);
+    return launch_linear_b1_planes(planes, w, bias, y, M, &shrunk, st);
 }
 
 }  // namespace sbvr
