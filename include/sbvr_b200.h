@@ -46,7 +46,8 @@ enum {
     SBVR_ERR_CUDA = -4,               /* a CUDA runtime call failed; see sbvr_last_cuda_error */
     SBVR_ERR_WORKSPACE = -5,          /* workspace missing or too small for this call */
     SBVR_ERR_TIMEOUT = -6,            /* a bounded device-side wait ran out (read by sbvr_workspace_status) */
-    SBVR_ERR_UNSUPPORTED = -7         /* valid arguments, but no kernel covers the combination */
+    SBVR_ERR_UNSUPPORTED = -7,        /* valid arguments, but no kernel covers the combination */
+    SBVR_ERR_NOALLOC_LIMIT = -8       /* sbvr_linear_f16_noalloc: the problem needs more than its fixed 4 MiB of scratch */
 };
 
 /* Text for a status code.  Replaces the reference's `throw std::runtime_error(cudaGetErrorString)`
@@ -110,6 +111,22 @@ SBVR_API int sbvr_linear_planes_f16(const void* planes, const uint32_t* bvr, con
 SBVR_API int sbvr_linear_f16_host(const void* x_host, const uint32_t* bvr, const void* coeff_idx, int idx_bytes,
                          const void* coeff, int C, const void* bias, void* y_host, int M, int N, int K, int S,
                          int G, int algo, sbvr_workspace_t* ws, sbvr_stream_t stream);
+
+/* The same product as sbvr_linear_f16 (algo 0) for callers that must not allocate device memory: hosts that
+ * own every byte of the GPU and forbid plugins to call cudaMalloc, latency-critical loops that cannot afford the
+ * allocator's implicit device synchronisation, code running next to an open stream capture.  It takes no
+ * workspace: the kernels' scratch is a fixed 4 MiB array inside the library's device image (held by every GPU that
+ * loads the library, until exit), and neither this call nor anything under it allocates or frees.
+ *   - Calls on one device share that array: calls that can overlap on the GPU race; serialise them.
+ *   - The first call on a device resolves the array's address and sets kernel attributes: make it outside stream
+ *     capture, with that device current.
+ *   - Problems whose scratch exceeds the array return SBVR_ERR_NOALLOC_LIMIT and launch nothing (all Llama-3
+ *     8B/70B layer shapes at M <= 4 fit).
+ * It has no counterpart in the reference, whose bindings allocate their output on every call
+ * (sbvr/kernels/sbvr_ops.cpp:100-101). */
+SBVR_API int sbvr_linear_f16_noalloc(const void* x, const uint32_t* bvr, const void* coeff_idx, int idx_bytes,
+                                     const void* coeff, int C, const void* bias, void* y, int M, int N, int K, int S,
+                                     int G, sbvr_stream_t stream);
 
 /* Test hook (host only, no GPU): the tile partition of the persistent GEMV grid.  No reference counterpart. */
 SBVR_API int sbvr_debug_b1_partition(int T, int P, int c, int* begin, int* end, int t, int* owner);

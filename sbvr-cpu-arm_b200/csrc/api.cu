@@ -60,6 +60,9 @@ const char* sbvr_strerror(int status) {
         case SBVR_ERR_WORKSPACE: return "workspace missing or too small";
         case SBVR_ERR_TIMEOUT: return "a bounded device-side wait ran out";
         case SBVR_ERR_UNSUPPORTED: return "no kernel covers this combination of arguments";
+        case SBVR_ERR_NOALLOC_LIMIT:
+            return "the problem needs more scratch than the fixed 4 MiB array of sbvr_linear_f16_noalloc; use "
+                   "sbvr_linear_f16 with a workspace";
         default: return "unknown status";
     }
 }

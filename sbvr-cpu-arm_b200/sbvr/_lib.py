@@ -49,7 +49,10 @@ lib.sbvr_act_planes_f16.restype = _i
 lib.sbvr_linear_planes_f16.argtypes = [_vp, _vp, _vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp]
 lib.sbvr_linear_planes_f16.restype = _i
 
-EXPORTS = ["sbvr_strerror", "sbvr_last_cuda_error", "sbvr_query", "sbvr_workspace_create",
+lib.sbvr_linear_f16_noalloc.argtypes = [_vp, _vp, _vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp]
+lib.sbvr_linear_f16_noalloc.restype = _i
+
+EXPORTS = ["sbvr_linear_f16_noalloc", "sbvr_strerror", "sbvr_last_cuda_error", "sbvr_query", "sbvr_workspace_create",
            "sbvr_workspace_destroy", "sbvr_workspace_status", "sbvr_decode_f16", "sbvr_linear_f16",
            "sbvr_linear_f16_host", "sbvr_debug_b1_partition", "sbvr_act_planes_bytes", "sbvr_act_planes_f16",
            "sbvr_linear_planes_f16"]
