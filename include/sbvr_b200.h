@@ -61,7 +61,7 @@ SBVR_API int sbvr_last_cuda_error(void);
  * bound at :153), which cached cudaDeviceProp for every device and printed them.  Any out pointer may be NULL. */
 SBVR_API int sbvr_query(int device, int* sm_count, int* smem_per_block_optin, int* l2_bytes, int* cc_major, int* cc_minor);
 
-/* Scratch memory for split-K partial sums, the quantised activation planes and the device status word.
+/* Scratch memory: the device status word of the bounded waits, staging buffers of the host-pointer entry point.
  * The reference allocates nothing comparable (its kernels keep everything in registers); it does allocate
  * the output inside the binding (sbvr/kernels/sbvr_ops.cpp:100-101), which here is the caller's job.
  * `bytes` = 0 picks a default that covers every Llama-3 8B/70B layer shape up to 32 activation rows.
@@ -85,25 +85,11 @@ SBVR_API int sbvr_decode_f16(const uint32_t* bvr, const void* coeff_idx, int idx
  * Llama flow runs (sbvr_utils/utils_llama.py:147, test_sbvr.py:321).  K must be the padded length
  * (multiple of G).  `ws` may be NULL only for the kernels that need no scratch (see `algo`).
  *   algo 0 = pick; 1 = SIMT dequantise-and-FMA kernel (any S <= 8, no workspace);
- *   2 = bit-serial mma.sync b1 kernel (S in {2,3,4}, M <= 4, needs workspace; emulated on sm_100, kept as a cross-check);
- *   3 = tcgen05 FP4 tensor-core kernel (S in {2,3,4}, M <= 4, N a multiple of 32 (64 for S = 2), needs workspace). */
+ *   2 = tcgen05 FP4 tensor-core kernel (S in {2,3,4}, M <= 4, N a multiple of 32 (64 for S = 2), needs a workspace
+ *       for its status word). */
 SBVR_API int sbvr_linear_f16(const void* x, const uint32_t* bvr, const void* coeff_idx, int idx_bytes, const void* coeff,
                     int C, const void* bias, void* y, int M, int N, int K, int S, int G, int algo,
                     sbvr_workspace_t* ws, sbvr_stream_t stream);
-
-/* The two halves of sbvr_linear_f16's tensor-core kernel (algo 3), for callers that feed several layers
- * from one activation (q/k/v, gate/up) and want to quantise it once.
- *   sbvr_act_planes_bytes : size of the digits buffer for M <= 4 rows of K activations (0 = unsupported).
- *   sbvr_act_planes_f16   : fp16 x[M, K] -> 16-bit block fixed point (one power-of-two step per group of G)
- *                           as eight radix-4 E2M1 digit planes, written to `planes` (device, 256-byte aligned).
- *   sbvr_linear_planes_f16: the product from such a buffer.  Same result as sbvr_linear_f16(algo 3).
- * The reference has no counterpart for activations held as planes with fp16 weights' planes; its nearest
- * relative is the SBVR-encoded left operand of `_sbvr_mm_T` (sbvr/kernels/sbvr_ops.cpp:35-76). */
-SBVR_API size_t sbvr_act_planes_bytes(int M, int K, int G);
-SBVR_API int sbvr_act_planes_f16(const void* x, void* planes, int M, int K, int G, sbvr_stream_t stream);
-SBVR_API int sbvr_linear_planes_f16(const void* planes, const uint32_t* bvr, const void* coeff_idx, int idx_bytes,
-                                    const void* coeff, int C, const void* bias, void* y, int M, int N, int K, int S,
-                                    int G, sbvr_workspace_t* ws, sbvr_stream_t stream);
 
 /* Same product with HOST x and y: copies x in, runs sbvr_linear_f16, copies y out, all on `stream`
  * (weights stay on the device).  The end-to-end form of the call the reference binding makes with a
@@ -127,9 +113,6 @@ SBVR_API int sbvr_linear_f16_host(const void* x_host, const uint32_t* bvr, const
 SBVR_API int sbvr_linear_f16_noalloc(const void* x, const uint32_t* bvr, const void* coeff_idx, int idx_bytes,
                                      const void* coeff, int C, const void* bias, void* y, int M, int N, int K, int S,
                                      int G, sbvr_stream_t stream);
-
-/* Test hook (host only, no GPU): the tile partition of the persistent GEMV grid.  No reference counterpart. */
-SBVR_API int sbvr_debug_b1_partition(int T, int P, int c, int* begin, int* end, int t, int* owner);
 
 #ifdef __cplusplus
 }

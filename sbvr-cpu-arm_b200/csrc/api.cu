@@ -1,5 +1,5 @@
 // C ABI of sbvr_b200: argument validation, workspace management and dispatch.  Nothing here
-// computes; see decode.cu, linear_simt.cu, linear_b1.cu.
+// computes; see decode.cu, linear_simt.cu, linear_tc.cu.
 #include <mutex>
 
 #include "common.cuh"
@@ -161,7 +161,7 @@ int sbvr_linear_f16(const void* x, const uint32_t* bvr, const void* coeff_idx, i
     if (rc) return rc;
     if (!x || !y || M < 1) return SBVR_ERR_BAD_ARG;
     if ((reinterpret_cast<uintptr_t>(x) & 3) || (reinterpret_cast<uintptr_t>(y) & 1)) return SBVR_ERR_ALIGN;
-    if (algo < 0 || algo > 3) return SBVR_ERR_BAD_ARG;
+    if (algo < 0 || algo > 2) return SBVR_ERR_BAD_ARG;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     const __half* xh = reinterpret_cast<const __half*>(x);
     const __half* bh = reinterpret_cast<const __half*>(bias);
@@ -169,33 +169,10 @@ int sbvr_linear_f16(const void* x, const uint32_t* bvr, const void* coeff_idx, i
     if (algo == 0) {
         DeviceInfo di;
         algo = 1;
-        if (ws && linear_tc_supported(w, M) && device_info(ws->device, &di) == SBVR_OK && di.cc_major == 10) algo = 3;
+        if (ws && linear_tc_supported(w, M) && device_info(ws->device, &di) == SBVR_OK && di.cc_major == 10) algo = 2;
     }
-    if (algo == 3) return launch_linear_tc(xh, w, bh, yh, M, ws, st);
-    if (algo == 2) return launch_linear_b1(xh, w, bh, yh, M, ws, st);
+    if (algo == 2) return launch_linear_tc(xh, w, bh, yh, M, ws, st);
     return launch_linear_simt(xh, w, bh, yh, M, st);
-}
-
-size_t sbvr_act_planes_bytes(int M, int K, int G) {
-    if (M < 1 || M > 4 || K < 256 || K % 256 || (G != 256 && G != 128)) return 0;
-    return act_digits_bytes(M, K, G);
-}
-
-int sbvr_act_planes_f16(const void* x, void* planes, int M, int K, int G, sbvr_stream_t stream) {
-    if (!x || !planes || M < 1 || K < 1) return SBVR_ERR_BAD_ARG;
-    if (K % 256) return SBVR_ERR_SHAPE;
-    return launch_xdigits(reinterpret_cast<const __half*>(x), planes, M, K, G, reinterpret_cast<cudaStream_t>(stream));
-}
-
-int sbvr_linear_planes_f16(const void* planes, const uint32_t* bvr, const void* coeff_idx, int idx_bytes,
-                           const void* coeff, int C, const void* bias, void* y, int M, int N, int K, int S, int G,
-                           sbvr_workspace_t* ws, sbvr_stream_t stream) {
-    PackedW w;
-    int rc = make_packed(&w, bvr, coeff_idx, idx_bytes, coeff, C, N, K, S, G);
-    if (rc) return rc;
-    if (!planes || !y || M < 1) return SBVR_ERR_BAD_ARG;
-    return launch_linear_tc_digits(planes, w, reinterpret_cast<const __half*>(bias), reinterpret_cast<__half*>(y), M,
-                                   ws, reinterpret_cast<cudaStream_t>(stream));
 }
 
 int sbvr_linear_f16_host(const void* x_host, const uint32_t* bvr, const void* coeff_idx, int idx_bytes,

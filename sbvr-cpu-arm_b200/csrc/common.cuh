@@ -53,8 +53,8 @@ struct sbvr_workspace {
     char* base;               // device
     // fixed regions at the start of `base`
     unsigned int* status;     // [4]   word 0: 0 ok / 1 a bounded wait ran out; word 1: where
-    unsigned int* counters;   // [SBVR_WS_COUNTERS] arrival counters of split-K row tiles, all zero between calls
-    char* dyn;                // rest: activation planes, partial sums
+    unsigned int* counters;   // [SBVR_WS_COUNTERS] reserved for kernels that count arrivals; all zero between calls
+    char* dyn;                // rest: staging buffers of the host-pointer entry point, future scratch
     size_t dyn_bytes;
     void* pinned_status;      // host, 16 bytes
 };
@@ -64,20 +64,9 @@ namespace sbvr {
 
 int launch_decode(const PackedW& w, __half* W, int ldw, int Kout, cudaStream_t st);
 int launch_linear_simt(const __half* x, const PackedW& w, const __half* bias, __half* y, int M, cudaStream_t st);
-int launch_linear_b1(const __half* x, const PackedW& w, const __half* bias, __half* y, int M,
-                     sbvr_workspace* ws, cudaStream_t st);
-bool linear_b1_supported(const PackedW& w, int M);
 bool linear_tc_supported(const PackedW& w, int M);
-size_t act_digits_bytes(int M, int K, int G);
-int launch_xdigits(const __half* x, void* buf, int M, int K, int G, cudaStream_t st);
-int launch_linear_tc_digits(const void* buf, const PackedW& w, const __half* bias, __half* y, int M,
-                            sbvr_workspace* ws, cudaStream_t st);
 int launch_linear_tc(const __half* x, const PackedW& w, const __half* bias, __half* y, int M,
                      sbvr_workspace* ws, cudaStream_t st);
-size_t act_planes_bytes(int M, int K, int G);
-int launch_xquant(const __half* x, void* planes, int M, int K, int G, cudaStream_t st);
-int launch_linear_b1_planes(const void* planes, const PackedW& w, const __half* bias, __half* y, int M,
-                            sbvr_workspace* ws, cudaStream_t st);
 
 // ---------------------------------------------------------------------------------------------
 // device side
@@ -135,6 +124,28 @@ __device__ __forceinline__ bool mbar_wait_timed(uint64_t* bar, uint32_t parity) 
             "selp.b32 %0, 1, 0, p;\n\t}"
             : "=r"(ok)
             : "r"(a), "r"(parity), "r"(100000u)
+            : "memory");
+        if (ok) return true;
+        if (t0 == 0) t0 = clock64();
+        else if (clock64() - t0 > 2000000000LL) return false;
+    }
+}
+
+// Bounded wait for barriers completed by ASYNCHRONOUS arrivals (tcgen05.commit, bulk-copy complete_tx).
+// Measured on B200: a waiter parked by try_wait with a long suspend hint is woken promptly by a
+// thread's mbarrier.arrive, but sleeps on for thousands of cycles when the phase is completed by an
+// asynchronous arrival.  So these barriers are polled with the default (short) time limit.
+__device__ __forceinline__ bool mbar_wait_async(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    const uint32_t a = smem_u32(bar);
+    long long t0 = 0;
+    for (;;) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.b32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(a), "r"(parity)
             : "memory");
         if (ok) return true;
         if (t0 == 0) t0 = clock64();

@@ -40,22 +40,12 @@ lib.sbvr_linear_f16.argtypes = [_vp, _vp, _vp, _i, _vp, _i, _vp, _vp, _i, _i, _i
 lib.sbvr_linear_f16.restype = _i
 lib.sbvr_linear_f16_host.argtypes = [_vp, _vp, _vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp]
 lib.sbvr_linear_f16_host.restype = _i
-lib.sbvr_debug_b1_partition.argtypes = [_i, _i, _i, _ip, _ip, _i, _ip]
-lib.sbvr_debug_b1_partition.restype = _i
-lib.sbvr_act_planes_bytes.argtypes = [_i, _i, _i]
-lib.sbvr_act_planes_bytes.restype = _sz
-lib.sbvr_act_planes_f16.argtypes = [_vp, _vp, _i, _i, _i, _vp]
-lib.sbvr_act_planes_f16.restype = _i
-lib.sbvr_linear_planes_f16.argtypes = [_vp, _vp, _vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp]
-lib.sbvr_linear_planes_f16.restype = _i
-
 lib.sbvr_linear_f16_noalloc.argtypes = [_vp, _vp, _vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp]
 lib.sbvr_linear_f16_noalloc.restype = _i
 
 EXPORTS = ["sbvr_linear_f16_noalloc", "sbvr_strerror", "sbvr_last_cuda_error", "sbvr_query", "sbvr_workspace_create",
            "sbvr_workspace_destroy", "sbvr_workspace_status", "sbvr_decode_f16", "sbvr_linear_f16",
-           "sbvr_linear_f16_host", "sbvr_debug_b1_partition", "sbvr_act_planes_bytes", "sbvr_act_planes_f16",
-           "sbvr_linear_planes_f16"]
+           "sbvr_linear_f16_host"]
 
 
 def strerror(rc: int) -> str:
