@@ -68,6 +68,11 @@ SBVR_API int sbvr_query(int device, int* sm_count, int* smem_per_block_optin, in
  * One workspace must not be used by two calls that can overlap on the GPU. */
 SBVR_API int sbvr_workspace_create(sbvr_workspace_t** ws, int device, size_t bytes);
 SBVR_API int sbvr_workspace_destroy(sbvr_workspace_t* ws);
+/* Bytes to ask sbvr_workspace_create for so that every kernel (and the host-pointer entry point) can serve
+ * linears of up to M activation rows on an N x K weight: the batched kernel keeps a re-tiled copy of the
+ * activations (M x K fp16, M rounded up to its tile) and, when it splits K, fp32 partial sums.  No reference
+ * counterpart (the reference has no scratch). */
+SBVR_API int sbvr_workspace_bytes(int device, int M, int N, int K, size_t* bytes);
 /* Synchronises `stream`, then reads the device status word: SBVR_OK or SBVR_ERR_TIMEOUT. Resets it. */
 SBVR_API int sbvr_workspace_status(sbvr_workspace_t* ws, sbvr_stream_t stream);
 
@@ -85,8 +90,10 @@ SBVR_API int sbvr_decode_f16(const uint32_t* bvr, const void* coeff_idx, int idx
  * Llama flow runs (sbvr_utils/utils_llama.py:147, test_sbvr.py:321).  K must be the padded length
  * (multiple of G).  `ws` may be NULL only for the kernels that need no scratch (see `algo`).
  *   algo 0 = pick; 1 = SIMT dequantise-and-FMA kernel (any S <= 8, no workspace);
- *   2 = tcgen05 FP4 tensor-core kernel (S in {2,3,4}, M <= 4, N a multiple of 32 (64 for S = 2), needs a workspace
- *       for its status word). */
+ *   2 = tcgen05 FP4 tensor-core kernel for decode (S in {2,3,4}, M <= 4, N a multiple of 32 (64 for S = 2),
+ *       K a multiple of 256; needs a workspace for its status word);
+ *   3 = tcgen05 fp16 GEMM with in-kernel dequantisation for batches and prefill (S in {2,3,4}, any M,
+ *       N a multiple of 128; needs a workspace of sbvr_workspace_bytes(...)). */
 SBVR_API int sbvr_linear_f16(const void* x, const uint32_t* bvr, const void* coeff_idx, int idx_bytes, const void* coeff,
                     int C, const void* bias, void* y, int M, int N, int K, int S, int G, int algo,
                     sbvr_workspace_t* ws, sbvr_stream_t stream);
@@ -113,6 +120,45 @@ SBVR_API int sbvr_linear_f16_host(const void* x_host, const uint32_t* bvr, const
 SBVR_API int sbvr_linear_f16_noalloc(const void* x, const uint32_t* bvr, const void* coeff_idx, int idx_bytes,
                                      const void* coeff, int C, const void* bias, void* y, int M, int N, int K, int S,
                                      int G, sbvr_stream_t stream);
+
+/* ---- the kernels between the linears of a Llama decoder layer ----------------------------------------------
+ * Each replaces a chain of eager PyTorch ops of the reference model (models/sbvr_llama.py) by one launch.
+ * All tensors fp16, contiguous, 16-byte aligned unless noted. */
+
+/* h_out = h_in + delta (fp16 add; delta NULL = no add; h_out NULL = not stored, may equal h_in);
+ * y = weight * fp16(h_out * rsqrt(mean(h_out^2) + eps)).  LlamaRMSNorm.forward (models/sbvr_llama.py:118-123)
+ * with the residual add of LlamaDecoderLayer.forward (:395-406) folded in.  hidden % 8 == 0. */
+SBVR_API int sbvr_add_rmsnorm_f16(const void* h_in, const void* delta, const void* weight, void* h_out, void* y,
+                                  int rows, int hidden, float eps, sbvr_stream_t stream);
+
+/* Rotary embedding of the q and k parts of fused rows qkv[tokens][(n_heads + 2 n_kv) * head_dim], in place, and
+ * append of the rotated k and of v to the caches [seqs][n_kv][max_ctx][head_dim] at positions[token]
+ * (int32; sequence = token / tokens_per_seq).  cos/sin = fp16(cos|sin(pos * inv_freq[i]) * attn_scaling),
+ * products and sum in fp16: LlamaRotaryEmbedding.forward, rotate_half, apply_rotary_pos_emb
+ * (models/sbvr_llama.py:169-224) and the cache update of LlamaAttention.forward (:330-336). */
+SBVR_API int sbvr_rope_append_f16(void* qkv, const int* positions, const float* inv_freq, float attn_scaling,
+                                  void* kcache, void* vcache, int tokens, int tokens_per_seq, int n_heads, int n_kv,
+                                  int head_dim, int max_ctx, sbvr_stream_t stream);
+
+/* out[token][head][:] = softmax(q . K^T * scale) . V over cache positions 0 .. positions[token] of the token's
+ * sequence, grouped-query (n_heads % n_kv == 0, ratio 1, 2, 4 or 8), head_dim 128.  Serves decode (one token per
+ * sequence) and causal prefill (every token attends up to itself; its k, v must be in the cache already).
+ * nsplit > 1 splits the positions over CTAs (decode at long context) and needs `scratch` of
+ * tokens * n_heads * nsplit * 130 floats.  repeat_kv + eager_attention_forward (models/sbvr_llama.py:243-278). */
+SBVR_API int sbvr_attention_f16(const void* qkv, const void* kcache, const void* vcache, const int* positions,
+                                void* out, float* scratch, int tokens, int tokens_per_seq, int n_heads, int n_kv,
+                                int head_dim, int max_ctx, float scale, int nsplit, sbvr_stream_t stream);
+
+/* out[row][i] = fp16(silu(gate[row][i])) * up[row][i] with gate_up[row] = [gate (inter) | up (inter)]:
+ * the activation of LlamaMLP.forward (models/sbvr_llama.py:238-240) on a fused gate/up linear.  inter % 8 == 0. */
+SBVR_API int sbvr_silu_mul_f16(const void* gate_up, void* out, int rows, int inter, sbvr_stream_t stream);
+
+/* out[token][:] = table[ids[token]][:]  (nn.Embedding of LlamaModel, models/sbvr_llama.py:568-672). */
+SBVR_API int sbvr_embedding_f16(const int* ids, const void* table, void* out, int tokens, int hidden,
+                                sbvr_stream_t stream);
+
+/* out[row] = index of the first maximum of logits[row][0 .. vocab-1] (greedy decoding; torch.argmax's tie rule). */
+SBVR_API int sbvr_argmax_f16(const void* logits, int* out, int rows, int vocab, sbvr_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -116,6 +116,21 @@ int sbvr_workspace_create(sbvr_workspace_t** out, int device, size_t bytes) {
     return SBVR_OK;
 }
 
+int sbvr_workspace_bytes(int device, int M, int N, int K, size_t* bytes) {
+    if (!bytes || M < 1 || N < 1 || K < 1) return SBVR_ERR_BAD_ARG;
+    DeviceInfo di;
+    int rc = device_info(device, &di);
+    if (rc) return rc;
+    PackedW w;
+    w.bvr = nullptr, w.idx = nullptr, w.coeff = nullptr, w.idx_bytes = 0, w.C = 0;
+    w.N = N, w.K = K, w.S = 4, w.G = 256;
+    const size_t fixed = 256 + (size_t)SBVR_WS_COUNTERS * 4;
+    const size_t stage = (((size_t)M * K * 2 + 255) / 256 + ((size_t)M * N * 2 + 255) / 256) * 256;   // host-pointer staging
+    *bytes = fixed + linear_gemm_workspace_bytes(w, M, di.sm_count) + stage + ((size_t)8 << 20);
+    if (*bytes < ((size_t)32 << 20)) *bytes = (size_t)32 << 20;
+    return SBVR_OK;
+}
+
 int sbvr_workspace_destroy(sbvr_workspace_t* ws) {
     if (!ws) return SBVR_OK;
     int prev = 0;
@@ -161,7 +176,7 @@ int sbvr_linear_f16(const void* x, const uint32_t* bvr, const void* coeff_idx, i
     if (rc) return rc;
     if (!x || !y || M < 1) return SBVR_ERR_BAD_ARG;
     if ((reinterpret_cast<uintptr_t>(x) & 3) || (reinterpret_cast<uintptr_t>(y) & 1)) return SBVR_ERR_ALIGN;
-    if (algo < 0 || algo > 2) return SBVR_ERR_BAD_ARG;
+    if (algo < 0 || algo > 3) return SBVR_ERR_BAD_ARG;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     const __half* xh = reinterpret_cast<const __half*>(x);
     const __half* bh = reinterpret_cast<const __half*>(bias);
@@ -169,9 +184,14 @@ int sbvr_linear_f16(const void* x, const uint32_t* bvr, const void* coeff_idx, i
     if (algo == 0) {
         DeviceInfo di;
         algo = 1;
-        if (ws && linear_tc_supported(w, M) && device_info(ws->device, &di) == SBVR_OK && di.cc_major == 10) algo = 2;
+        if (ws && device_info(ws->device, &di) == SBVR_OK && di.cc_major == 10) {
+            if (linear_tc_supported(w, M) && !(reinterpret_cast<uintptr_t>(x) & 15)) algo = 2;
+            else if (linear_gemm_supported(w, M) &&
+                     linear_gemm_workspace_bytes(w, M, di.sm_count) <= ws->dyn_bytes) algo = 3;
+        }
     }
     if (algo == 2) return launch_linear_tc(xh, w, bh, yh, M, ws, st);
+    if (algo == 3) return launch_linear_gemm(xh, w, bh, yh, M, ws, st);
     return launch_linear_simt(xh, w, bh, yh, M, st);
 }
 

@@ -67,6 +67,10 @@ int launch_linear_simt(const __half* x, const PackedW& w, const __half* bias, __
 bool linear_tc_supported(const PackedW& w, int M);
 int launch_linear_tc(const __half* x, const PackedW& w, const __half* bias, __half* y, int M,
                      sbvr_workspace* ws, cudaStream_t st);
+bool linear_gemm_supported(const PackedW& w, int M);
+size_t linear_gemm_workspace_bytes(const PackedW& w, int M, int sm_count);
+int launch_linear_gemm(const __half* x, const PackedW& w, const __half* bias, __half* y, int M,
+                       sbvr_workspace* ws, cudaStream_t st);
 
 // ---------------------------------------------------------------------------------------------
 // device side

@@ -136,7 +136,7 @@ __device__ __forceinline__ void tc_ld8(uint32_t taddr, float (&d)[8]) {
 
 // Optional timestamp trace of thread 0 of CTA 0 (development builds only, -DSBVR_PROFILE).
 #ifdef SBVR_PROFILE
-__device__ long long g_tc_prof[8 * 64 + 8];
+__device__ long long g_tc_prof[8 * 64 + 16];
 __device__ long long g_tc_iprof[4 * 64];
 #define TC_PROF(slot)                                                                                             \
     do {                                                                                                          \
@@ -201,15 +201,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1) linear_tc_kernel(const TcParams
     const int G = (int)gridDim.x;
     const int n_units = ((int)blockIdx.x < p.NT) ? (p.NT - 1 - (int)blockIdx.x) / G + 1 : 0;   // row tiles of this CTA
 
-    if (threadIdx.x == 0) {
-        for (int i = 0; i < 3 * TC_WGS; ++i) mbar_init(&mma_bar[i], 1);
-        for (int i = 0; i < 2 * TC_WGS; ++i) mbar_init(&a_ready[i], 4);
-        for (int i = 0; i < 2; ++i) mbar_init(&red_full[i], TC_WGS * 4);
-        for (int i = 0; i < 2; ++i) mbar_init(&red_empty[i], 1);
-        mbar_init(b_ready, TC_WGS * 4);
-        mbar_init(tmem_ready, 1);
-        mbar_init(cache_bar, 1);
-        flags[0] = 0;
+    if (threadIdx.x < 5 * TC_WGS + 7) {            // one barrier per thread: the barriers are contiguous
+        const int i = threadIdx.x;
+        const uint32_t count = (i < 3 * TC_WGS)       ? 1u
+                               : (i < 5 * TC_WGS)     ? 4u
+                               : (i < 5 * TC_WGS + 2) ? (uint32_t)(TC_WGS * 4)
+                               : (i < 5 * TC_WGS + 4) ? 1u
+                               : (i == 5 * TC_WGS + 4) ? (uint32_t)(TC_WGS * 4)
+                                                       : 1u;
+        mbar_init(&mma_bar[i], count);
+        if (i == 0) flags[0] = 0;
         fence_mbar_init();
     }
     __syncthreads();                               // barriers are initialised; nothing else is waited for here
@@ -402,23 +403,47 @@ __global__ void __launch_bounds__(TC_THREADS, 1) linear_tc_kernel(const TcParams
                 ioff_l = (uint32_t)(my_lo * NSUB) * N + irow_l;
             }
         };
+        // ---- set-up shared by the CTA.  First the activations, copied as they are into the first half of each
+        // block's digit area (the oldest cp.async group), then the packed words of the first three tiles.
+        {
+            const int nchunk = M * KB * 32;        // 16-byte pieces
+            for (int c = ctid; c < nchunk; c += TC_CTHREADS) {
+                const int part = c & 31, blk = c >> 5;     // blk = m * KB + kb
+                const int m = blk / KB, kb = blk - m * KB;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(
+                                 smem_u32(Bs + ((size_t)kb * M + m) * 1024 + part * 16)),
+                             "l"(p.x + (size_t)m * p.K + (size_t)kb * 256 + part * 8)
+                             : "memory");
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        }
+        TC_PROF_MARK(10);
         Raw X0, X1, X2, X3;
         load_tile(X0);
+        TC_PROF_MARK(11);
         load_tile(X1);
         load_tile(X2);
-
-        // ---- set-up shared by the CTA.  The activation digits come first: their loads are the longest chain.
+        TC_PROF_MARK(5);
+        asm volatile("cp.async.wait_group 3;" ::: "memory");       // this thread's pieces of x have landed
+        named_bar_sync(2, TC_CTHREADS);                            // ... and everybody else's
+        TC_PROF_MARK(6);
         {
             // Activations -> radix-4 E2M1 digits.  One warp per 256-k block; lane (kw, j) owns the eight
             // elements k = 32 kw + j + 4 e, which are exactly one 32-bit word of every digit plane.
             const int kw = lane >> 2, j = lane & 3;
-            // E2M1 codes of digit value t (index t & 3), scaled by 2, 1, 0.5, 0.5 for j = 0..3;
-            // low digits take t in {0,1,2,3}, the top digit t in {0,1,-2,-1}
-            const uint32_t lut_lo = (j == 0) ? 0x7640u : (j == 1) ? 0x5420u : 0x3210u;
-            const uint32_t lut_hi = (j == 0) ? 0xCE40u : (j == 1) ? 0xAC20u : 0x9A10u;
+            // E2M1 codes of digit value t = 0..3 as bytes, scaled by 2, 1, 0.5, 0.5 for j = 0..3; the low digits
+            // take t as {0,1,2,3}, the top digit as {0,1,-2,-1}
+            const uint32_t pool_lo = (j == 0) ? 0x07060400u : (j == 1) ? 0x05040200u : 0x03020100u;
+            const uint32_t pool_hi = (j == 0) ? 0x0C0E0400u : (j == 1) ? 0x0A0C0200u : 0x090A0100u;
+            // Digit words are stored rotated by kw (word i of this lane is digit (i + kw) & 7) so that the eight
+            // kw of a warp hit different banks; the rotation is applied to the digits themselves, which keeps
+            // every register index static.  `top` marks the nibble that holds digit 7 after the rotation.
+            const uint32_t rot = 4u * (uint32_t)kw;
+            const uint32_t top = 4u << (4u * (uint32_t)(7 - kw));
             for (int blk = warp; blk < M * KB; blk += TC_WGS * 4) {
                 const int m = blk / KB, kb = blk - m * KB;
-                const __half* xp = p.x + (size_t)m * p.K + (size_t)kb * 256 + 32 * kw + j;
+                unsigned char* area = Bs + ((size_t)kb * M + m) * 1024;
+                const __half* xp = reinterpret_cast<const __half*>(area) + 32 * kw + j;
                 float v[8];
                 float a = 0.0f;
 #pragma unroll
@@ -428,8 +453,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) linear_tc_kernel(const TcParams
                     if (!(av == av)) av = __int_as_float(0x7f800000);     // NaN counts as infinity
                     a = fmaxf(a, av);
                 }
+                __syncwarp();                      // all lanes hold their elements: the area may be overwritten
+                TC_PROF_MARK(12);
 #pragma unroll
                 for (int o = (NSUB == 2 ? 8 : 16); o; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+                TC_PROF_MARK(13);
                 float step = 0.0f, inv = 0.0f;
                 bool poison = false;
                 if (a >= __int_as_float(0x7f800000)) {                    // non-finite activations poison the group
@@ -445,26 +473,36 @@ __global__ void __launch_bounds__(TC_THREADS, 1) linear_tc_kernel(const TcParams
                 } else {
                     if ((lane & 15) == 0) xsc[(m * KB + kb) * 2 + (lane >> 4)] = step;
                 }
-                uint32_t q4[8];                                           // 16-bit two's complement, shifted left by 2
+                // per element: 16-bit two's complement -> its 8 radix-4 digits, one per nibble -> rotate -> codes
+                uint32_t c_lo[8], c_hi[8];         // bytes i = 0..3 / 4..7: code of rotated digit i
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
-                    const int q = poison ? 1 : __float2int_rn(v[e] * inv);           // |q| < 2^15
-                    q4[e] = ((uint32_t)q & 0xFFFFu) << 2;
+                    const uint32_t q = poison ? 1u : (uint32_t)__float2int_rn(v[e] * inv);     // |q| < 2^15
+                    uint32_t sp = __byte_perm(q, 0u, 0x4140);                 // bytes [q0, 0, q1, 0]
+                    sp = (sp | (sp << 4)) & 0x0F0F0F0Fu;
+                    sp = (sp | (sp << 2)) & 0x33333333u;                      // nibble d = digit d
+                    sp = __funnelshift_r(sp, sp, rot) | top;                  // nibble i = digit (i + kw) & 7; top digit + 4
+                    c_lo[e] = __byte_perm(pool_lo, pool_hi, sp);
+                    c_hi[e] = __byte_perm(pool_lo, pool_hi, sp >> 16);
                 }
-                uint32_t* dstw = reinterpret_cast<uint32_t*>(Bs + ((size_t)kb * M + m) * 1024) + kw * 32 + j;
+                TC_PROF_MARK(14);
+                // element pairs share a byte (low nibble = even element), then a 4 x 4 byte transpose per half
+                uint32_t* dstw = reinterpret_cast<uint32_t*>(area) + kw * 32 + j;
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const int d = (i + kw) & 7;    // rotated so that the eight kw of a warp hit different banks
-                    const uint32_t lut = (d == 7) ? lut_hi : lut_lo;
-                    uint32_t word = 0;
+                for (int hf = 0; hf < 2; ++hf) {
+                    uint32_t R[4];
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) {
-                        const uint32_t sh = (q4[e] >> (2 * d)) & 0xCu;    // 4 * digit
-                        word |= ((lut >> sh) & 0xFu) << (4 * e);
-                    }
-                    dstw[d * 4] = word;            // [kw][d][16 B], word j
+                    for (int pr = 0; pr < 4; ++pr)
+                        R[pr] = hf ? (c_hi[2 * pr] | (c_hi[2 * pr + 1] << 4)) : (c_lo[2 * pr] | (c_lo[2 * pr + 1] << 4));
+                    const uint32_t t0 = __byte_perm(R[0], R[1], 0x5140), t1 = __byte_perm(R[2], R[3], 0x5140);
+                    const uint32_t t2 = __byte_perm(R[0], R[1], 0x7362), t3 = __byte_perm(R[2], R[3], 0x7362);
+                    const uint32_t T[4] = {__byte_perm(t0, t1, 0x5410), __byte_perm(t0, t1, 0x7632),
+                                           __byte_perm(t2, t3, 0x5410), __byte_perm(t2, t3, 0x7632)};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) dstw[(((hf * 4 + i) + kw) & 7) * 4] = T[i];   // [kw][digit][16 B], word j
                 }
             }
+            TC_PROF_MARK(7);
             fence_proxy_async();                   // generic writes of the digits -> visible to the MMA's reads
             __syncwarp();
             if (lane == 0) mbar_arrive(b_ready);
@@ -478,6 +516,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) linear_tc_kernel(const TcParams
         }
         bool dead = !wait_tmem();
         dead = __any_sync(0xffffffffu, dead);
+        TC_PROF_MARK(8);
         const uint32_t tbase = *tmem_base_s;
         const uint32_t a_col = tbase + wg * TC_WG_COLS;
         const uint32_t d_col = a_col + (PIPE ? 64 : 32);
@@ -488,6 +527,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) linear_tc_kernel(const TcParams
         tc_fence_before();
         named_bar_sync(1, TC_CTHREADS);            // scale factors, steps, hand-copied codebook and digits are in place
         tc_fence_after();
+        TC_PROF_MARK(9);
         if (bulk_cache && !mbar_wait_async(cache_bar, 0u)) dead = true;
         dead = __any_sync(0xffffffffu, dead);
         if (dead) flags[0] = 1;
@@ -747,6 +787,7 @@ int launch_linear_tc(const __half* x, const PackedW& w, const __half* bias, __ha
                      cudaStream_t st) {
     if (!linear_tc_supported(w, M)) return SBVR_ERR_UNSUPPORTED;
     if (!ws) return SBVR_ERR_WORKSPACE;
+    if (reinterpret_cast<uintptr_t>(x) & 15) return SBVR_ERR_ALIGN;      // x is fetched with 16-byte cp.async
     DeviceInfo di;
     int rc = device_info(ws->device, &di);
     if (rc) return rc;
@@ -769,9 +810,9 @@ int launch_linear_tc(const __half* x, const PackedW& w, const __half* bias, __ha
 
 #ifdef SBVR_PROFILE
 extern "C" __attribute__((visibility("default"))) int sbvr_debug_read_profile(long long* out, int n) {
-    long long tmp[8 * 64 + 8];
+    long long tmp[8 * 64 + 16];
     if (cudaMemcpyFromSymbol(tmp, sbvr::g_tc_prof, sizeof(tmp)) != cudaSuccess) return -1;
-    for (int i = 0; i < n && i < 8 * 64 + 8; ++i) out[i] = tmp[i];
+    for (int i = 0; i < n && i < 8 * 64 + 16; ++i) out[i] = tmp[i];
     return 0;
 }
 extern "C" __attribute__((visibility("default"))) int sbvr_debug_read_iprofile(long long* out, int n) {

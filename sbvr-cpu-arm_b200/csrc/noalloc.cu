@@ -93,7 +93,7 @@ extern "C" int sbvr_linear_f16_noalloc(const void* x, const uint32_t* bvr, const
     DeviceInfo di;
     rc = device_info(dev, &di);
     if (rc) return rc;
-    if (di.cc_major != 10 || !linear_tc_supported(w, M))
+    if (di.cc_major != 10 || !linear_tc_supported(w, M) || (reinterpret_cast<uintptr_t>(x) & 15))
         return launch_linear_simt(xh, w, bh, yh, M, st);      // this kernel needs no scratch at all
 
     // carve the static array exactly like an allocated workspace

@@ -1,0 +1,1 @@
+"""Llama on SBVR linears (`SBVRLinear`, `SBVRLlamaForCausalLM`) and the slicing helpers of its tensor-parallel form."""

@@ -30,6 +30,8 @@ lib.sbvr_query.argtypes = [_i, _ip, _ip, _ip, _ip, _ip]
 lib.sbvr_query.restype = _i
 lib.sbvr_workspace_create.argtypes = [ctypes.POINTER(_vp), _i, _sz]
 lib.sbvr_workspace_create.restype = _i
+lib.sbvr_workspace_bytes.argtypes = [_i, _i, _i, _i, ctypes.POINTER(_sz)]
+lib.sbvr_workspace_bytes.restype = _i
 lib.sbvr_workspace_destroy.argtypes = [_vp]
 lib.sbvr_workspace_destroy.restype = _i
 lib.sbvr_workspace_status.argtypes = [_vp, _vp]
@@ -43,7 +45,22 @@ lib.sbvr_linear_f16_host.restype = _i
 lib.sbvr_linear_f16_noalloc.argtypes = [_vp, _vp, _vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp]
 lib.sbvr_linear_f16_noalloc.restype = _i
 
-EXPORTS = ["sbvr_linear_f16_noalloc", "sbvr_strerror", "sbvr_last_cuda_error", "sbvr_query", "sbvr_workspace_create",
+_f = ctypes.c_float
+lib.sbvr_add_rmsnorm_f16.argtypes = [_vp, _vp, _vp, _vp, _vp, _i, _i, _f, _vp]
+lib.sbvr_add_rmsnorm_f16.restype = _i
+lib.sbvr_rope_append_f16.argtypes = [_vp, _vp, _vp, _f, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]
+lib.sbvr_rope_append_f16.restype = _i
+lib.sbvr_attention_f16.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp]
+lib.sbvr_attention_f16.restype = _i
+lib.sbvr_silu_mul_f16.argtypes = [_vp, _vp, _i, _i, _vp]
+lib.sbvr_silu_mul_f16.restype = _i
+lib.sbvr_embedding_f16.argtypes = [_vp, _vp, _vp, _i, _i, _vp]
+lib.sbvr_embedding_f16.restype = _i
+lib.sbvr_argmax_f16.argtypes = [_vp, _vp, _i, _i, _vp]
+lib.sbvr_argmax_f16.restype = _i
+
+EXPORTS = ["sbvr_add_rmsnorm_f16", "sbvr_rope_append_f16", "sbvr_attention_f16", "sbvr_silu_mul_f16",
+           "sbvr_embedding_f16", "sbvr_argmax_f16", "sbvr_linear_f16_noalloc", "sbvr_workspace_bytes", "sbvr_strerror", "sbvr_last_cuda_error", "sbvr_query", "sbvr_workspace_create",
            "sbvr_workspace_destroy", "sbvr_workspace_status", "sbvr_decode_f16", "sbvr_linear_f16",
            "sbvr_linear_f16_host"]
 
@@ -68,11 +85,15 @@ def query(device: int = 0) -> dict:
 
 
 class Workspace:
-    """Owns one `sbvr_workspace_t` (device scratch for split-K partial sums and activation planes)."""
+    """Owns one `sbvr_workspace_t`: the device status word of the kernels' bounded waits, the re-tiled
+    activations and split-K partial sums of the batched kernel, staging buffers of the host-pointer call."""
+
+    DEFAULT_BYTES = 32 << 20
 
     def __init__(self, device: int, nbytes: int = 0):
         self.handle = _vp()
         self.device = device
+        self.nbytes = nbytes or self.DEFAULT_BYTES
         check(lib.sbvr_workspace_create(ctypes.byref(self.handle), device, nbytes), "sbvr_workspace_create")
 
     def status(self, stream: int) -> int:
@@ -93,11 +114,24 @@ class Workspace:
 _workspaces: dict = {}
 
 
-def workspace(device: int, stream: int) -> Workspace:
-    """One workspace per (device, stream): calls on one stream are ordered, so they may share scratch."""
+def workspace_bytes(device: int, M: int, N: int, K: int) -> int:
+    out = _sz(0)
+    check(lib.sbvr_workspace_bytes(device, M, N, K, ctypes.byref(out)), "sbvr_workspace_bytes")
+    return out.value
+
+
+def workspace(device: int, stream: int, nbytes: int = 0) -> Workspace:
+    """One workspace per (device, stream): calls on one stream are ordered, so they may share scratch.
+    A workspace smaller than `nbytes` is replaced by a larger one (after the stream has drained)."""
     key = (device, stream)
     ws = _workspaces.get(key)
+    if ws is not None and ws.nbytes < nbytes:
+        import torch
+        with torch.cuda.device(device):
+            torch.cuda.synchronize()
+        ws.close()
+        ws = None
     if ws is None:
-        ws = Workspace(device)
+        ws = Workspace(device, max(nbytes, Workspace.DEFAULT_BYTES))
         _workspaces[key] = ws
     return ws

@@ -301,7 +301,7 @@ def linear(x: torch.Tensor, w: sbvr, bias: Optional[torch.Tensor] = None, algo: 
     b, ix, ib, c, C = w._abi_args()
     with torch.cuda.device(di):
         st = torch.cuda.current_stream().cuda_stream
-        ws = _lib.workspace(di, st)
+        ws = _lib.workspace(di, st, _lib.workspace_bytes(di, M, N, Kp) if M > 4 else 0)
         _lib.check(_lib.lib.sbvr_linear_f16(x2.data_ptr(), b, ix, ib, c, C, _ptr(bias), y.data_ptr(), M, N, Kp,
                                             w.num_sums, w.bvr_len, algo, ws.handle, st), "sbvr_linear_f16")
     return y.view(*lead, N)

