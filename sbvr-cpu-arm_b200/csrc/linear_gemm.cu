@@ -252,25 +252,32 @@ __global__ void __launch_bounds__(GM_THREADS, 1) linear_gemm_kernel(const GmPara
         const int dtid = threadIdx.x;              // 0 .. 383
         const uint32_t lane_sel = (uint32_t)(wl * 32) << 16;
         const int N = p.N;
-        const int stages_per_group = p.G / 64;
         bool dead = false;
 
         // The stages of all work items of this CTA form one sequence; this warpgroup takes every third one.
         struct Pos {
             int item, ks, it;
+            int kst0, n;                           // first 64-k stage of the item's k part; this thread's weight row
+        };
+        auto set_item = [&](Pos& q) {              // the divisions happen once per work item, not per stage
+            q.kst0 = (q.item % p.KS) * SPP;
+            q.n = (q.item / (p.KS * p.MT)) * 128 + r;
         };
         auto advance = [&](Pos& q, int by) {
             q.ks += by;
             q.it += by;
-            while (q.ks >= SPP) {
-                q.ks -= SPP;
-                q.item += grid;
+            if (q.ks >= SPP) {
+                do {
+                    q.ks -= SPP;
+                    q.item += grid;
+                } while (q.ks >= SPP);
+                set_item(q);
             }
         };
+        const int group_shift = (p.G == 256) ? 2 : 1;      // 64-k stages per coefficient group, as a shift
         auto load_words = [&](const Pos& q, uint32_t (&w)[2][S]) {
             if (q.item >= p.items) return;
-            const int kp = q.item % p.KS, nt = q.item / (p.KS * p.MT);
-            const uint32_t* src = p.bvr + ((size_t)(2 * (kp * SPP + q.ks)) * N + nt * 128 + r) * S;
+            const uint32_t* src = p.bvr + ((size_t)(2 * (q.kst0 + q.ks)) * N + q.n) * S;
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 const uint32_t* g = src + (size_t)h * N * S;
@@ -357,9 +364,8 @@ __global__ void __launch_bounds__(GM_THREADS, 1) linear_gemm_kernel(const GmPara
         // coefficient line itself one step before (it needs the index), so neither latency is exposed.
         auto line_of = [&](const Pos& q) -> uint32_t {
             if (q.item >= p.items) return 0u;
-            const int kp = q.item % p.KS, nt = q.item / (p.KS * p.MT);
-            const int g = (kp * SPP + q.ks) / stages_per_group;
-            const size_t e = (size_t)g * N + nt * 128 + r;
+            const int g = (q.kst0 + q.ks) >> group_shift;
+            const size_t e = (size_t)g * N + q.n;
             if (p.idx_bytes == 1) return __ldg(reinterpret_cast<const uint8_t*>(p.idx) + e);
             if (p.idx_bytes == 2) return __ldg(reinterpret_cast<const uint16_t*>(p.idx) + e);
             return (uint32_t)e;
@@ -371,7 +377,8 @@ __global__ void __launch_bounds__(GM_THREADS, 1) linear_gemm_kernel(const GmPara
             for (int s = 0; s < S; ++s) c[s] = __ldg(src + s);
         };
 
-        Pos cur{(int)blockIdx.x, 0, 0};
+        Pos cur{(int)blockIdx.x, 0, 0, 0, 0};
+        set_item(cur);
         advance(cur, wg);
         Pos nxt = cur;
         advance(nxt, GM_DWGS);

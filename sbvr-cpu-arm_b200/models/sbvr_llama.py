@@ -366,7 +366,8 @@ class SBVRLlamaForCausalLM(torch.nn.Module):
                 self._forward_rows(b, 1, last_only=True)
             s.synchronize()
             g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=s):
+            # thread_local: other threads (the NCCL watchdog) may touch the CUDA API while this one captures
+            with torch.cuda.graph(g, stream=s, capture_error_mode="thread_local"):
                 self._forward_rows(b, 1, last_only=True)
                 b.ids.copy_(b.next_ids)
                 b.positions.add_(1)

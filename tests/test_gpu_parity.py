@@ -244,3 +244,19 @@ def test_host_buffer_entry_point():
     ref = O.linear_c(x.numpy(), p["bvr"], p["coeff_idx"], p["coeff"], G=256)
     assert O.max_rel_err(y.numpy(), ref) <= TOL
     check_status()
+
+
+@pytest.mark.parametrize("K", [256, 512, 768])
+@pytest.mark.parametrize("M", [1, 2])
+def test_linear_fewer_k_blocks_than_warpgroups(K, M):
+    """Row-parallel shards of small models leave a CTA fewer 256-k blocks than it has compute warpgroups."""
+    import sbvr
+    N, S = 512, 4
+    p = O.make_packed(N, K, S, G=256, mode="u8", seed=K + M)
+    w = to_sbvr(p)
+    rng = np.random.default_rng(K)
+    x = rng.standard_normal((M, K)).astype(np.float16)
+    ref = O.linear_c(x, p["bvr"], p["coeff_idx"], p["coeff"], G=256)
+    y = h2n(sbvr.linear(torch.from_numpy(x).cuda(), w, None, algo=2))
+    assert O.max_rel_err(y, ref) <= TOL
+    check_status()

@@ -1,0 +1,79 @@
+"""Tensor-parallel SBVR Llama (one process per GPU, NCCL) against the single-GPU model.  The one-rank case runs
+the same collectives and their capture into the decode graph on a single GPU; the two-rank case is skipped when
+fewer than two GPUs are visible.  Children report exceptions instead of leaving their peers waiting."""
+import datetime
+import os
+import sys
+import traceback
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+pytestmark = pytest.mark.gpu
+
+
+def _worker(rank, world, port, q):
+    try:
+        sys.path.insert(0, ROOT)
+        sys.path.insert(0, os.path.join(ROOT, "sbvr-cpu-arm_b200"))
+        os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+        os.environ["NCCL_NVLS_ENABLE"] = "0"
+        import torch.distributed as dist
+        from models.sbvr_llama import LlamaConfig, SBVRLlamaForCausalLM
+        torch.cuda.set_device(rank)
+        dev = torch.device("cuda", rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev,
+                                timeout=datetime.timedelta(seconds=90))
+        cfg = LlamaConfig.preset("tiny")
+        tp = SBVRLlamaForCausalLM(cfg, device=dev, tp_group=dist.group.WORLD, max_batch=2, max_ctx=64).init_synthetic(3)
+        ids = torch.randint(0, cfg.vocab_size, (2, 24), device=dev, generator=torch.Generator(device=dev).manual_seed(9))
+        logits = tp(ids).float()
+        a = tp.generate(ids, 10, use_graph=False)
+        b = tp.generate(ids, 10, use_graph=True)
+        same = bool(torch.equal(a, b))
+        err = -1.0
+        if rank == 0:
+            one = SBVRLlamaForCausalLM(cfg, device=dev, max_batch=2, max_ctx=64).init_synthetic(3)
+            ref = one(ids).float()
+            err = ((logits - ref).abs().max() / ref.abs().max()).item()
+        q.put((rank, "ok", err, same))
+        dist.destroy_process_group()
+    except Exception:
+        q.put((rank, "error", traceback.format_exc(), False))
+
+
+def _run(world):
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29500 + (os.getpid() + 7 * world) % 2000
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = []
+    try:
+        for _ in range(world):
+            results.append(q.get(timeout=240))
+            if results[-1][1] != "ok":
+                break
+    finally:
+        for p in procs:
+            p.join(20)
+            if p.is_alive():
+                p.terminate()
+    for r in results:
+        assert r[1] == "ok", r[2]
+    assert len(results) == world
+    r0 = [r for r in results if r[0] == 0][0]
+    assert r0[2] <= 1e-2, r0[2]
+    assert all(r[3] for r in results)
+
+
+def test_one_rank_group_runs_collectives_and_graph():
+    _run(1)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_gpu_tensor_parallel_matches_single_gpu():
+    _run(2)
