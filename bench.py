@@ -219,6 +219,14 @@ def run_ours(args):
             t = torch.tensor([e2e_s], device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             e2e_s = float(t.item())
+    extra = {}
+    if not args.no_extras:
+        if world == 1:
+            extra.update(small_m_and_prefill(torch, dev, stream))
+        decodes = [llama_decode(torch, dev, dist, world, "8b", 1, 512, 256)]
+        if not args.skip_70b:
+            decodes.append(llama_decode(torch, dev, dist, world, "70b", 1, 1024, 256))
+        extra["llama_decode"] = decodes
     for (d, s_), w in _lib._workspaces.items():
         assert w.status(s_) == 0, "a device-side wait timed out during the benchmark"
 
@@ -251,10 +259,119 @@ def run_ours(args):
         "gpu_launches": args.steps * len(SHAPES),
         "clocks": clocks,
     }
+    line.update(extra)
     line["cpu_baseline"] = cpu_baseline()
     print(json.dumps(line), flush=True)
     if dist:
         dist.destroy_process_group()
+
+
+def graph_time_us(torch, stream, fns, reps=5):
+    """Average device time of one call of the functions in `fns`, replayed from one CUDA graph."""
+    with torch.cuda.stream(stream):
+        for f in fns:
+            f()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            for f in fns:
+                f()
+        g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(reps):
+            g.replay()
+        e1.record(stream)
+        e1.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / reps / len(fns)
+
+
+def small_m_and_prefill(torch, dev, stream):
+    """BASELINE configs 1 and 2 beside the headline: the M sweep of the layer shapes (HBM roofline) and the
+    M = 2048 prefill GEMM (tensor roofline).  Every timing cycles through more weights than L2 holds."""
+    import sbvr
+    peak, _ = measured_peak()
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            tf_peak = float(json.load(f)["bf16_tflops"])
+    except Exception:
+        tf_peak = 1590.0
+    gen = torch.Generator(device=dev).manual_seed(11)
+
+    def mk(N, K):
+        bvr = torch.randint(-2**31, 2**31 - 1, (K // 32, N, S), dtype=torch.int32, device=dev, generator=gen)
+        idx = torch.randint(0, C, (K // G, N), device=dev, generator=gen).to(torch.int16).view(torch.uint16)
+        cache = (torch.randn((C, S), device=dev, generator=gen) * 0.01).half()
+        return sbvr.sbvr.from_packed(bvr, idx, cache, group_len=G, device=dev)
+    sweep, prefill = [], []
+    for N, K in [(4096, 4096), (1024, 4096), (14336, 4096), (4096, 14336)]:
+        ncopy = int(2 * 126e6 / (N * K * S / 8)) + 2
+        ws_ = [mk(N, K) for _ in range(ncopy)]
+        for M in (1, 4, 16, 32):
+            x = torch.randn((M, K), device=dev, generator=gen).half()
+            outs = [torch.empty((M, N), dtype=torch.float16, device=dev) for _ in range(ncopy)]
+            us = graph_time_us(torch, stream, [(lambda w=w, o=o: sbvr.linear(x, w, None, out=o)) for w, o in zip(ws_, outs)])
+            gbs = alg_bytes(M, N, K) / us / 1e3
+            sweep.append({"N": N, "K": K, "M": M, "us": round(us, 2), "GBps": round(gbs, 1), "frac": round(gbs / peak, 4)})
+        if N * K == 14336 * 4096:
+            M = 2048
+            x = torch.randn((M, K), device=dev, generator=gen).half()
+            out = torch.empty((M, N), dtype=torch.float16, device=dev)
+            us = graph_time_us(torch, stream, [(lambda w=w: sbvr.linear(x, w, None, out=out)) for w in ws_[:4]])
+            tf = 2.0 * M * N * K / us / 1e6
+            prefill.append({"N": N, "K": K, "M": M, "us": round(us, 1), "TFLOPs": round(tf, 1),
+                            "frac_of_measured_bf16_burst": round(tf / tf_peak, 4)})
+        del ws_
+    return {"small_m_sweep": {"S": S, "G": G, "rows": sweep}, "prefill_gemm": prefill}
+
+
+def llama_decode(torch, dev, dist, world, preset, batch, prompt, new_tokens):
+    """Tokens/s of greedy decoding (CUDA-graph replay of one step) of the SBVR Llama, tensor parallel over all
+    ranks of the job; the prompt is prefilled first and timed separately."""
+    from models.sbvr_llama import LlamaConfig, SBVRLlamaForCausalLM
+    cfg = LlamaConfig.preset(preset)
+    group = dist.group.WORLD if dist else None
+    m = SBVRLlamaForCausalLM(cfg, device=dev, tp_group=group, max_batch=batch, max_ctx=prompt + new_tokens + 8)
+    m.init_synthetic(7)
+    ids = torch.randint(0, cfg.vocab_size, (batch, prompt), device=dev, generator=torch.Generator(device=dev).manual_seed(99))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    m.prefill(ids)
+    torch.cuda.synchronize()
+    e0.record()
+    nxt = m.prefill(ids)
+    e1.record()
+    torch.cuda.synchronize()
+    prefill_ms = e0.elapsed_time(e1)
+    m.generate(ids, 4)                                 # captures the decode graph
+    b = m._act(batch, batch)
+    with torch.inference_mode():
+        b.ids.copy_(nxt)
+        b.positions.fill_(prompt)
+    torch.cuda.synchronize()
+    if dist:
+        dist.barrier()
+    e0.record()
+    for _ in range(new_tokens):
+        m._graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    if dist:
+        t = torch.tensor([ms, prefill_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, prefill_ms = float(t[0].item()), float(t[1].item())
+    m._check()
+    wbytes = m.packed_weight_bytes()
+    peak, _ = measured_peak()
+    res = {"model": preset, "tp": world, "batch": batch, "prompt": prompt, "new_tokens": new_tokens,
+           "tokens_per_s": round(batch * new_tokens / ms * 1e3, 1), "ms_per_step": round(ms / new_tokens, 4),
+           "prefill_ms": round(prefill_ms, 2), "packed_weight_bytes_per_gpu": wbytes,
+           "weight_stream_GBps_per_gpu": round(wbytes / (ms / new_tokens) / 1e6, 1),
+           "frac_of_hbm_roofline": round(wbytes / (ms / new_tokens) / 1e6 / peak, 4)}
+    del m
+    torch.cuda.empty_cache()
+    return res
 
 
 def cpu_baseline(reps=None):
@@ -302,13 +419,43 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def kernel_case(which):
+    """Six 14336 x 4096 weights (176 MB, more than L2), two warm-up rounds, then one launch per weight."""
+    import torch
+    import sbvr
+    dev = torch.device("cuda", 0)
+    gen = torch.Generator(device=dev).manual_seed(7)
+    N, K = 14336, 4096
+    M = {"gemv": 1, "gemm16": 16, "gemm2048": 2048}[which]
+    ws_ = []
+    for _ in range(6):
+        bvr = torch.randint(-2**31, 2**31 - 1, (K // 32, N, S), dtype=torch.int32, device=dev, generator=gen)
+        idx = torch.randint(0, C, (K // G, N), device=dev, generator=gen).to(torch.int16).view(torch.uint16)
+        cache = (torch.randn((C, S), device=dev, generator=gen) * 0.01).half()
+        ws_.append(sbvr.sbvr.from_packed(bvr, idx, cache, group_len=G, device=dev))
+    x = torch.randn((M, K), device=dev, generator=gen).half()
+    y = torch.empty((M, N), dtype=torch.float16, device=dev)
+    for _ in range(3):
+        for w in ws_:
+            sbvr.linear(x, w, None, out=y)
+    torch.cuda.synchronize()
+    print(json.dumps({"kernel_case": which, "launches": 18, "mean_abs_y": float(y.float().abs().mean())}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-extras", action="store_true",
+                    help="only the headline GEMV measurement (no M sweep, prefill GEMM or Llama decode sections)")
+    ap.add_argument("--skip-70b", action="store_true", help="leave the 70B decode out of the Llama section")
+    ap.add_argument("--kernel-case", default=None, choices=["gemv", "gemm16", "gemm2048"],
+                    help="run a few launches of one kernel on 14336x4096 weights and exit (for profilers)")
     args = ap.parse_args()
+    if args.kernel_case:
+        return kernel_case(args.kernel_case)
     if args.impl == "reference":
         run_reference(args)
     else:
