@@ -59,7 +59,8 @@ constexpr int TC_WG_COLS = 112;                 // tensor-memory columns per war
 constexpr int TC_SF_COL = 448;                  // 32 columns of unit scale factors
 constexpr int TC_BSLACK = 4096;                 // MMA columns beyond M read (and ignore) what follows
 constexpr int TC_STAGES = 4;                    // packed words of the next three tiles are in flight per warpgroup
-constexpr int TC_RING_BYTES = TC_WGS * TC_STAGES * 8 * 128 * 4;
+constexpr int TC_STAGE_BYTES = 1152;              // per warp and stage: 8 x 128 B of packed words + 128 B of coefficient data
+constexpr int TC_RING_BYTES = TC_WGS * 4 * TC_STAGES * TC_STAGE_BYTES;
 
 struct TcParams {
     const __half* x;
@@ -352,56 +353,58 @@ __global__ void __launch_bounds__(TC_THREADS, 1) linear_tc_kernel(const TcParams
         const int per_unit = my_hi - my_lo;
         const int n_tiles = per_unit * n_units;
 
-        // ---- loads run three tiles ahead.  The packed words go global -> shared memory with per-thread
-        // 4-byte cp.async (every thread copies, and later reads back, only its own row's words, so
-        // cp.async.wait_group is all the synchronisation needed and no register scoreboard is tied up
-        // for a memory latency); 32-bit element offsets, advanced incrementally.
-        struct Raw {
-            uint32_t ci[NSUB];
-        };
-        const uint32_t NS = (uint32_t)N * S, KSTEP = 8u * NS, ISTEP = (uint32_t)NSUB * N;
-        const uint32_t USTEP = (uint32_t)G * TN * S, UISTEP = (uint32_t)G * TN;   // next row tile of this CTA
+        // ---- loads run three tiles ahead, global -> shared memory with cp.async, one ring per warp.  A warp
+        // needs, per 256-k tile, 8 rows (one per 32 k) of 128 contiguous bytes (96 for S = 3) and the coefficient
+        // indices (or direct coefficients) of its 32 MMA rows: 64 (48) pieces of 16 bytes, two per lane, plus up
+        // to 8 pieces of 8 bytes.  Lanes copy for each other, so a __syncwarp follows the wait; no register
+        // scoreboard is tied up for a memory latency.  Byte offsets are 32-bit and advance by constants.
+        constexpr int CPR = (S == 3) ? 6 : 8;                  // 16-byte pieces per 32-k row of a warp
+        constexpr int WROW = CPR * 16;                         // bytes of such a row
+        constexpr int CI_PIECES = (IDXB == 0) ? (32 / SP) * S * 2 / 8 : ((32 / SP) * IDXB + 7) / 8;   // 8-byte pieces per sub
+        constexpr int CI_BYTES = (IDXB == 0) ? (32 / SP) * S * 2 : (32 / SP) * IDXB;
+        constexpr int STAGE_B = TC_STAGE_BYTES;                // 1024 B of words + 128 B of coefficient data
+        const uint32_t ROWB = (uint32_t)N * S * 4;             // bytes between the rows of consecutive 32-k words
+        const uint32_t KSTEP_B = 8u * ROWB;
+        const uint32_t CIROW = (IDXB == 0) ? (uint32_t)N * S * 2 : (uint32_t)N * IDXB;     // bytes per coefficient group
+        const uint32_t ISTEP_B = (uint32_t)NSUB * CIROW;
+        // from the last tile of a row tile to the first tile of this CTA's next row tile
+        const uint32_t WRAP_B = (uint32_t)G * TN * S * 4 - (uint32_t)(per_unit - 1) * KSTEP_B;
+        const uint32_t IWRAP_B = (uint32_t)G * TN * (CIROW / N) - (uint32_t)(per_unit - 1) * ISTEP_B;
         int kb_l = my_lo, loaded = 0;
-        uint32_t row_l = ((uint32_t)blockIdx.x * TN + nl) * S + s;                  // offsets of (row, plane) at kw = 0
-        uint32_t irow_l = (uint32_t)blockIdx.x * TN + nl;
-        uint32_t off_l = (uint32_t)(my_lo * 8) * NS + row_l;
-        uint32_t ioff_l = (uint32_t)(my_lo * NSUB) * N + irow_l;
-        uint32_t* my_ring = wring + (size_t)wg * TC_STAGES * 8 * 128 + r;            // [stage][kw][128 rows]
-        const uint32_t my_ring_s = smem_u32(my_ring);
-        auto load_tile = [&](Raw& q) {
-            if (loaded < n_tiles && live_row) {
-                const uint32_t dst = my_ring_s + (uint32_t)(loaded % TC_STAGES) * (8 * 128 * 4);
-#pragma unroll
-                for (int kw = 0; kw < 8; ++kw)
-                    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + kw * 512),
-                                 "l"(p.bvr + (off_l + kw * NS))
+        uint32_t off_l = ((uint32_t)(my_lo * 8) * N + (uint32_t)blockIdx.x * TN) * S * 4;
+        uint32_t ioff_l = (uint32_t)(my_lo * NSUB) * CIROW + (uint32_t)blockIdx.x * TN * (CIROW / N);
+        unsigned char* ring_w = reinterpret_cast<unsigned char*>(wring) + (size_t)warp * TC_STAGES * STAGE_B;
+        const uint32_t ring_s = smem_u32(ring_w);
+        const int c1 = lane + 32;                              // second 16-byte piece of this lane
+        const bool two = c1 < 8 * CPR;
+        const uint32_t rel0 = (uint32_t)(lane / CPR) * ROWB + (uint32_t)wl * WROW + (uint32_t)(lane % CPR) * 16;
+        const uint32_t rel1 = (uint32_t)(c1 / CPR) * ROWB + (uint32_t)wl * WROW + (uint32_t)(c1 % CPR) * 16;
+        const bool ci_lane = lane < NSUB * CI_PIECES;
+        const int ci_sub = lane / CI_PIECES, ci_pc = lane % CI_PIECES;
+        const uint32_t irel = (uint32_t)ci_sub * CIROW + (uint32_t)wl * CI_BYTES + (uint32_t)ci_pc * 8;
+        const unsigned char* wbytes = reinterpret_cast<const unsigned char*>(p.bvr);
+        const unsigned char* cbytes_g = (IDXB == 0) ? reinterpret_cast<const unsigned char*>(p.coeff)
+                                                    : reinterpret_cast<const unsigned char*>(p.idx);
+        auto load_tile = [&]() {
+            if (loaded < n_tiles) {
+                const uint32_t dst = ring_s + (uint32_t)(loaded % TC_STAGES) * STAGE_B;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + lane * 16), "l"(wbytes + (off_l + rel0))
+                             : "memory");
+                if (two)
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + c1 * 16),
+                                 "l"(wbytes + (off_l + rel1))
                                  : "memory");
-#pragma unroll
-                for (int sub = 0; sub < NSUB; ++sub) {
-                    const uint32_t io = ioff_l + sub * N;
-                    if constexpr (IDXB == 0)
-                        q.ci[sub] = __ldcs(reinterpret_cast<const unsigned short*>(p.coeff) + ((size_t)io * S + s));
-                    else if constexpr (IDXB == 1)
-                        q.ci[sub] = __ldcs(reinterpret_cast<const unsigned char*>(p.idx) + io);
-                    else
-                        q.ci[sub] = __ldcs(reinterpret_cast<const unsigned short*>(p.idx) + io);
-                }
-            } else {
-#pragma unroll
-                for (int sub = 0; sub < NSUB; ++sub) q.ci[sub] = 0u;
+                if (ci_lane)
+                    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst + 1024 + ci_sub * 64 + ci_pc * 8),
+                                 "l"(cbytes_g + (ioff_l + irel))
+                                 : "memory");
             }
             asm volatile("cp.async.commit_group;" ::: "memory");      // one group per tile, empty or not
             ++loaded;
-            ++kb_l;
-            off_l += KSTEP;
-            ioff_l += ISTEP;
-            if (kb_l == my_hi) {                   // on to this warpgroup's quarter of the CTA's next row tile
-                kb_l = my_lo;
-                row_l += USTEP;
-                irow_l += UISTEP;
-                off_l = (uint32_t)(my_lo * 8) * NS + row_l;
-                ioff_l = (uint32_t)(my_lo * NSUB) * N + irow_l;
-            }
+            const bool wrap = (++kb_l == my_hi);   // on to this warpgroup's quarter of the CTA's next row tile
+            off_l += wrap ? WRAP_B : KSTEP_B;
+            ioff_l += wrap ? IWRAP_B : ISTEP_B;
+            if (wrap) kb_l = my_lo;
         };
         // ---- set-up shared by the CTA.  First the activations, copied as they are into the first half of each
         // block's digit area (the oldest cp.async group), then the packed words of the first three tiles.
@@ -418,11 +421,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) linear_tc_kernel(const TcParams
             asm volatile("cp.async.commit_group;" ::: "memory");
         }
         TC_PROF_MARK(10);
-        Raw X0, X1, X2, X3;
-        load_tile(X0);
+        load_tile();
         TC_PROF_MARK(11);
-        load_tile(X1);
-        load_tile(X2);
+        load_tile();
+        load_tile();
         TC_PROF_MARK(5);
         asm volatile("cp.async.wait_group 3;" ::: "memory");       // this thread's pieces of x have landed
         named_bar_sync(2, TC_CTHREADS);                            // ... and everybody else's
@@ -536,13 +538,17 @@ __global__ void __launch_bounds__(TC_THREADS, 1) linear_tc_kernel(const TcParams
         float acc[M];
 #pragma unroll
         for (int m = 0; m < M; ++m) acc[m] = 0.0f;
-        uint32_t mph[3] = {0u, 0u, 0u};            // phases of this warpgroup's MMA barriers (one per D buffer)
-        uint32_t eph[2] = {0u, 0u};                // phases of the two "sums consumed" barriers
-        // epilogues run two tiles behind (PIPE): what they need of tiles ti-1 and ti-2, indexed by tile parity
-        float pscale[2][NSUB][M];
-        bool plast[2] = {false, false};
-        int pui[2] = {0, 0};
-        int ti = 0, kb_c = my_lo, ui_c = 0, dmod = 0;      // dmod = ti % 3 = D buffer of tile ti
+        uint32_t mph = 0u;                         // bit d: phase of this warpgroup's MMA barrier of D buffer d
+        uint32_t eph = 0u;                         // bit b: phase of "sums consumed" barrier b
+        // epilogues run two tiles behind (PIPE): what they need of tiles ti-1 (s1) and ti-2 (s2)
+        float s1[NSUB][M], s2[NSUB][M];
+        bool last1 = false, last2 = false;
+        int ui1 = 0, ui2 = 0;
+        int kb_c = my_lo, ui_c = 0, dmod = 0;      // dmod = ti % 3 = D buffer of tile ti
+#pragma unroll
+        for (int sub = 0; sub < NSUB; ++sub)
+#pragma unroll
+            for (int m = 0; m < M; ++m) s1[sub][m] = s2[sub][m] = 0.0f;
 
         // D of one finished tile -> fp32 sums.  `dbuf` selects the D buffer.
         auto epilogue = [&](int dbuf, const float (&scale)[NSUB][M]) {
@@ -561,13 +567,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) linear_tc_kernel(const TcParams
             tc_fence_before();     // order these tensor-memory reads before later writes of the buffer
         };
         auto wait_mma = [&](int dbuf) {
-            if (!dead && !mbar_wait_async(&mma_bar[wg * 3 + dbuf], mph[dbuf])) {
+            if (!dead && !mbar_wait_async(&mma_bar[wg * 3 + dbuf], (mph >> dbuf) & 1u)) {
                 dead = true;
                 flags[0] = 1;
             }
             dead = __any_sync(0xffffffffu, dead);  // warp-uniform: tcgen05.st/ld are .aligned
             if (!dead) {
-                mph[dbuf] ^= 1u;
+                mph ^= 1u << dbuf;
                 tc_fence_after();
             }
         };
@@ -575,12 +581,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) linear_tc_kernel(const TcParams
         auto deposit = [&](int ui) {
             const int ub = ui & 1;
             if (ui >= 2) {                         // the finisher must have consumed row tile ui - 2
-                if (!dead && !mbar_wait_timed(&red_empty[ub], eph[ub])) {
+                if (!dead && !mbar_wait_timed(&red_empty[ub], (eph >> ub) & 1u)) {
                     dead = true;
                     flags[0] = 1;
                 }
                 dead = __any_sync(0xffffffffu, dead);
-                eph[ub] ^= 1u;
+                eph ^= 1u << ub;
             }
             float* rs = red + (size_t)ub * TC_WGS * M * 128;
 #pragma unroll
@@ -591,44 +597,56 @@ __global__ void __launch_bounds__(TC_THREADS, 1) linear_tc_kernel(const TcParams
             __syncwarp();
             if (lane == 0) mbar_arrive(&red_full[ub]);
         };
-        // Wait for the MMAs of an earlier tile, fold its D into the sums, pass the sums on if it closed a row tile.
-        auto finish_tile = [&](int slot, int dbuf) {
-            wait_mma(dbuf);
-            if (!dead) epilogue(dbuf, pscale[slot]);
-            if (plast[slot]) deposit(pui[slot]);
-        };
 
-        // One tile: `cur` holds its coefficient index (loaded three steps ago), `fill` is the set to refill.
-        auto step = [&](Raw& cur, Raw& fill) {
+        if (per_unit == 0) {
+            // fewer k blocks than warpgroups: nothing to add, but the finisher still counts this warpgroup
+            for (int ui = 0; ui < n_units; ++ui) deposit(ui);
+        }
+        // word index of this thread's row inside a 32-k row of its warp's ring
+        const int wpos = (S == 3) ? 3 * (lane >> 2) + (lane & 3) : lane;
+        for (int ti = 0; ti < n_tiles; ++ti) {
             TC_PROF(0);
-            load_tile(fill);                       // tile ti + 3
+            load_tile();                           // tile ti + 3
             const int abuf = PIPE ? (ti & 1) : 0;
             TC_PROF(1);
+            TC_PROF(2);
+            // Tile ti-2: its MMAs were issued two tile times ago, so this wait rarely stalls; it also frees A
+            // buffer `abuf`, which those MMAs read.
+            if (PIPE && ti >= 2) {
+                const int db = (dmod == 2) ? 0 : dmod + 1;
+                wait_mma(db);
+                if (!dead) epilogue(db, s2);
+                if (last2) deposit(ui2);
+            }
+            TC_PROF(3);
+            // the copies of tile ti (issued three steps ago) have landed; three younger groups may be in flight
+            asm volatile("cp.async.wait_group 3;" ::: "memory");
+            __syncwarp();
+            const unsigned char* stg = ring_w + (size_t)(ti % TC_STAGES) * STAGE_B;
             float scale[NSUB][M];
 #pragma unroll
             for (int sub = 0; sub < NSUB; ++sub) {
                 float c = 0.0f;
                 if (live_row) {
-                    if constexpr (IDXB == 0) c = __half2float(__ushort_as_half((unsigned short)cur.ci[sub]));
-                    else c = __half2float((p.cache_in_smem ? cache_s : p.coeff)[(size_t)cur.ci[sub] * S + s]);
+                    const unsigned char* cs = stg + 1024 + sub * 64;
+                    if constexpr (IDXB == 0) {
+                        c = __half2float(reinterpret_cast<const __half*>(cs)[(lane / SP) * S + s]);
+                    } else {
+                        const uint32_t ci = (IDXB == 1) ? (uint32_t)cs[lane / SP]
+                                                        : (uint32_t)reinterpret_cast<const unsigned short*>(cs)[lane / SP];
+                        c = __half2float((p.cache_in_smem ? cache_s : p.coeff)[(size_t)ci * S + s]);
+                    }
                 }
 #pragma unroll
                 for (int m = 0; m < M; ++m) scale[sub][m] = c * xsc[(m * KB + kb_c) * NSUB + sub];
             }
-            TC_PROF(2);
-            // Tile ti-2: its MMAs were issued two tile times ago, so this wait does not stall; it also
-            // frees A buffer `abuf`, which those MMAs read.
-            if (PIPE && ti >= 2) finish_tile(ti & 1, dmod == 2 ? 0 : dmod + 1);
-            TC_PROF(3);
-            // the copies of tile ti (issued three steps ago) have landed; three younger groups may be in flight
-            asm volatile("cp.async.wait_group 3;" ::: "memory");
             if (!dead) {
                 // ---- packed words of this thread's row -> 32 words of 4-bit elements {0, 0.5 | 1 | 2 | 2}
-                const uint32_t* wsrc = my_ring + (size_t)(ti % TC_STAGES) * (8 * 128);
+                const uint32_t* wsrc = reinterpret_cast<const uint32_t*>(stg) + wpos;
                 uint32_t a[32];
 #pragma unroll
                 for (int kw = 0; kw < 8; ++kw) {
-                    const uint32_t w = (S == 3 && !live_row) ? 0u : wsrc[kw * 128];
+                    const uint32_t w = (S == 3 && !live_row) ? 0u : wsrc[kw * (WROW / 4)];
                     a[4 * kw + 0] = w & 0x11111111u;
                     a[4 * kw + 1] = w & 0x22222222u;
                     a[4 * kw + 2] = w & 0x44444444u;
@@ -644,13 +662,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1) linear_tc_kernel(const TcParams
             TC_PROF(5);
             const bool last_of_unit = (kb_c + 1 == my_hi);
             if (PIPE) {
-                const int slot = ti & 1;
 #pragma unroll
                 for (int sub = 0; sub < NSUB; ++sub)
 #pragma unroll
-                    for (int m = 0; m < M; ++m) pscale[slot][sub][m] = scale[sub][m];
-                plast[slot] = last_of_unit;
-                pui[slot] = ui_c;
+                    for (int m = 0; m < M; ++m) {
+                        s2[sub][m] = s1[sub][m];
+                        s1[sub][m] = scale[sub][m];
+                    }
+                last2 = last1, last1 = last_of_unit;
+                ui2 = ui1, ui1 = ui_c;
             } else {
                 wait_mma(0);
                 if (!dead) epilogue(0, scale);
@@ -658,32 +678,31 @@ __global__ void __launch_bounds__(TC_THREADS, 1) linear_tc_kernel(const TcParams
             }
             TC_PROF(6);
             TC_PROF_NEXT();
-            ++ti;
             dmod = (dmod == 2) ? 0 : dmod + 1;
-            ++kb_c;
-            if (kb_c == my_hi) {
+            if (last_of_unit) {
                 kb_c = my_lo;
                 ++ui_c;
+            } else {
+                ++kb_c;
             }
-            if ((ti & 7) == 0) {                   // notice a time-out elsewhere in the CTA now and then
+            if ((ti & 7) == 7) {                   // notice a time-out elsewhere in the CTA now and then
                 if (flags[0]) dead = true;
                 dead = __any_sync(0xffffffffu, dead);
             }
-        };
-
-        if (per_unit == 0) {
-            // fewer k blocks than warpgroups: nothing to add, but the finisher still counts this warpgroup
-            for (int ui = 0; ui < n_units; ++ui) deposit(ui);
-        }
-        while (ti < n_tiles) {
-            step(X0, X3);
-            if (ti < n_tiles) step(X1, X0);
-            if (ti < n_tiles) step(X2, X1);
-            if (ti < n_tiles) step(X3, X2);
         }
         if (PIPE) {                                // the last two tiles are still in the tensor pipe
-            if (n_tiles >= 2) finish_tile(n_tiles & 1, (n_tiles - 2) % 3);
-            if (n_tiles >= 1) finish_tile((n_tiles - 1) & 1, (n_tiles - 1) % 3);
+            if (n_tiles >= 2) {
+                const int db = (n_tiles - 2) % 3;
+                wait_mma(db);
+                if (!dead) epilogue(db, s2);
+                if (last2) deposit(ui2);
+            }
+            if (n_tiles >= 1) {
+                const int db = (n_tiles - 1) % 3;
+                wait_mma(db);
+                if (!dead) epilogue(db, s1);
+                if (last1) deposit(ui1);
+            }
         }
         asm volatile("cp.async.wait_all;" ::: "memory");
         if (dead) {
@@ -738,6 +757,8 @@ bool linear_tc_supported(const PackedW& w, int M) {
     if (w.N % tc_tn(w.S) || w.K % 256) return false;
     if (w.idx_bytes < 0 || w.idx_bytes > 2) return false;
     if (reinterpret_cast<uintptr_t>(w.coeff) & 15) return false;
+    if (reinterpret_cast<uintptr_t>(w.bvr) & 15) return false;                  // 16-byte cp.async of the packed words
+    if (w.idx_bytes && (reinterpret_cast<uintptr_t>(w.idx) & 7)) return false;   // 8-byte cp.async of the indices
     if ((size_t)w.N * w.K / 32 * w.S >= ((size_t)1 << 32)) return false;      // 32-bit word offsets
     // the activation digits of the whole K stay resident in shared memory: K/256 * M KB
     const int KB = w.K / 256, NSUB = 256 / w.G;
