@@ -160,6 +160,21 @@ SBVR_API int sbvr_embedding_f16(const int* ids, const void* table, void* out, in
 /* out[row] = index of the first maximum of logits[row][0 .. vocab-1] (greedy decoding; torch.argmax's tie rule). */
 SBVR_API int sbvr_argmax_f16(const void* logits, int* out, int rows, int vocab, sbvr_stream_t stream);
 
+/* ---- tensor parallel: one-shot all-reduce fused with the residual add and the RMSNorm ----------------------
+ * delta = fp16(sum over ranks of partial_r) (fp32, rank order), h_out = h_in + delta, y = RMSNorm(h_out) * weight,
+ * for the [rows, hidden] partial outputs that the row-parallel linears (o, down) of every rank wrote into buffer
+ * (call_idx & 1) of a symmetric allocation mapped by all ranks.  peer_bufs_dev / peer_flags_dev: device arrays of
+ * `world` 64-bit addresses (every rank's buffer area of 2 x buf_elems fp16, and its array of `world` zero-initialised
+ * uint32 flags).  step_dev: device int32 the caller increments once per model step; calls_per_step (even) and
+ * call_idx order the calls inside a step.  Peer data is read with plain loads over NVLink; waits on peers are
+ * bounded and report through the workspace status word.  For decode-sized batches; large batches should use NCCL.
+ * No counterpart in the reference (it has no tensor-parallel path); it takes the place of ncclAllReduce +
+ * the add and LlamaRMSNorm of models/sbvr_llama.py:118-123, :395-406. */
+SBVR_API int sbvr_allreduce_add_rmsnorm_f16(const void* peer_bufs_dev, const void* peer_flags_dev, const int* step_dev,
+                                            int calls_per_step, int call_idx, int rank, int world, size_t buf_elems,
+                                            const void* h_in, const void* weight, void* h_out, void* y, int rows,
+                                            int hidden, float eps, sbvr_workspace_t* ws, sbvr_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

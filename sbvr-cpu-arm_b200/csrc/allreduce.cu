@@ -1,0 +1,147 @@
+// One-shot all-reduce of the partial outputs of a row-parallel SBVR linear, fused with the residual add and the
+// RMSNorm that follow it in a Llama decoder layer:
+//
+//     delta = fp16( sum over ranks r = 0 .. world-1 of partial_r )      (fp32 sum, fixed rank order: every rank gets
+//     h_out = h_in + delta                                               the same bits, run after run)
+//     y     = weight * fp16( h_out * rsqrt(mean(h_out^2) + eps) )
+//
+// Replaces, for decode-sized batches, the NCCL all-reduce + residual add + LlamaRMSNorm of the tensor-parallel
+// model (reference models/sbvr_llama.py:118-123, :395-406; the reference itself has no tensor-parallel path).
+//
+// Every rank's linear writes its partial [rows, hidden] into its own buffer of a symmetric allocation that all
+// ranks have mapped (peer pointers are plain device pointers; the loads below are ordinary loads over NVLink, no
+// multicast).  Protocol per call, identified by a monotonically increasing epoch:
+//   1. block 0 publishes "my partial of this epoch is complete" by storing the epoch into slot [my rank] of every
+//      peer's flag array (system-scope release; the partial was written by the previous kernel on this stream);
+//   2. every block waits until all slots of its own flag array have reached the epoch (system-scope acquire),
+//      with a bounded number of polls: on time-out the status word is set and the block returns;
+//   3. every block reads its row from all ranks' buffers and finishes the three formulas above locally.
+// Two buffers alternate between consecutive calls: a rank can start call e + 2 (which overwrites the buffer of
+// call e) only after call e + 1, which needs every peer's flag of e + 1, which a peer raises only after its call e
+// has finished reading.  The epoch is step * calls_per_step + call + 1 with `step` read from device memory, so a
+// captured CUDA graph can be replayed: the host bumps `step` once per decode step inside the graph.
+#include "common.cuh"
+
+namespace sbvr {
+
+constexpr int AR_MAX_WORLD = 16;
+constexpr unsigned int AR_POLL_LIMIT = 1u << 22;        // polls of about 50 ns each
+
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+__global__ void __launch_bounds__(256) allreduce_add_rmsnorm_kernel(
+    const unsigned long long* __restrict__ peer_bufs,    // [world] base address of every rank's buffer area
+    const unsigned long long* __restrict__ peer_flags,   // [world] base address of every rank's flag array
+    const int* __restrict__ step_ptr, int calls_per_step, int call_idx, int rank, int world, size_t buf_elems,
+    const __half* h_in, const __half* __restrict__ weight, __half* h_out, __half* __restrict__ y, int hidden, float eps,
+    unsigned int* status) {
+    __shared__ float red[8];
+    __shared__ int ok_s;
+    const unsigned int epoch = (unsigned int)(*step_ptr) * (unsigned int)calls_per_step + (unsigned int)call_idx + 1u;
+    const size_t parity_off = (size_t)(call_idx & 1) * buf_elems;
+    if (blockIdx.x == 0 && threadIdx.x < world) {
+        __threadfence_system();
+        st_release_sys(reinterpret_cast<unsigned int*>(peer_flags[threadIdx.x]) + rank, epoch);
+    }
+    if (threadIdx.x == 0) ok_s = 1;
+    __syncthreads();
+    if (threadIdx.x < world) {
+        const unsigned int* mine = reinterpret_cast<const unsigned int*>(peer_flags[rank]) + threadIdx.x;
+        unsigned int n = 0;
+        // epochs only grow; a peer that is already one call ahead shows a larger value
+        while ((int)(ld_acquire_sys(mine) - epoch) < 0) {
+            if (++n > AR_POLL_LIMIT) {
+                ok_s = 0;
+                atomicExch(status, 1u);
+                atomicExch(status + 1, 0x700u + (unsigned int)rank);
+                break;
+            }
+            __nanosleep(40);
+        }
+    }
+    __syncthreads();
+    if (!ok_s) return;
+
+    const size_t row = (size_t)blockIdx.x * hidden;
+    const int nvec = hidden / 8;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+        float acc[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = 0.0f;
+        for (int r = 0; r < world; ++r) {
+            const __half* src = reinterpret_cast<const __half*>(peer_bufs[r]) + parity_off + row + (size_t)i * 8;
+            const uint4 v = __ldcv(reinterpret_cast<const uint4*>(src));
+            const __half2* vh = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 f = __half22float2(vh[e]);
+                acc[2 * e] += f.x, acc[2 * e + 1] += f.y;
+            }
+        }
+        uint4 a = *reinterpret_cast<const uint4*>(h_in + row + (size_t)i * 8);
+        __half2* ah = reinterpret_cast<__half2*>(&a);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            ah[e] = __hadd2(ah[e], __floats2half2_rn(acc[2 * e], acc[2 * e + 1]));
+            const float2 f = __half22float2(ah[e]);
+            ss += f.x * f.x + f.y * f.y;
+        }
+        *reinterpret_cast<uint4*>(h_out + row + (size_t)i * 8) = a;
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) tot += red[w];
+    const float rs = rsqrtf(tot / (float)hidden + eps);
+    for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+        const uint4 a = *reinterpret_cast<const uint4*>(h_out + row + (size_t)i * 8);     // written above by this thread
+        const uint4 wv = *reinterpret_cast<const uint4*>(weight + (size_t)i * 8);
+        const __half2* ah = reinterpret_cast<const __half2*>(&a);
+        const __half2* wh = reinterpret_cast<const __half2*>(&wv);
+        uint4 o;
+        __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = __half22float2(ah[e]);
+            oh[e] = __hmul2(wh[e], __floats2half2_rn(f.x * rs, f.y * rs));
+        }
+        *reinterpret_cast<uint4*>(y + row + (size_t)i * 8) = o;
+    }
+}
+
+}  // namespace sbvr
+
+using namespace sbvr;
+
+extern "C" int sbvr_allreduce_add_rmsnorm_f16(const void* peer_bufs_dev, const void* peer_flags_dev, const int* step_dev,
+                                               int calls_per_step, int call_idx, int rank, int world, size_t buf_elems,
+                                               const void* h_in, const void* weight, void* h_out, void* y, int rows,
+                                               int hidden, float eps, sbvr_workspace_t* ws, sbvr_stream_t stream) {
+    if (!peer_bufs_dev || !peer_flags_dev || !step_dev || !h_in || !weight || !h_out || !y || !ws) return SBVR_ERR_BAD_ARG;
+    if (world < 1 || world > AR_MAX_WORLD || rank < 0 || rank >= world || rows < 1 || calls_per_step < 1 || call_idx < 0 ||
+        call_idx >= calls_per_step || (calls_per_step & 1))
+        return SBVR_ERR_BAD_ARG;
+    if (hidden < 8 || hidden % 8) return SBVR_ERR_SHAPE;
+    if ((size_t)rows * hidden > buf_elems) return SBVR_ERR_WORKSPACE;
+    if ((reinterpret_cast<uintptr_t>(h_in) | reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(h_out) |
+         reinterpret_cast<uintptr_t>(y)) & 15)
+        return SBVR_ERR_ALIGN;
+    allreduce_add_rmsnorm_kernel<<<rows, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const unsigned long long*>(peer_bufs_dev), reinterpret_cast<const unsigned long long*>(peer_flags_dev),
+        step_dev, calls_per_step, call_idx, rank, world, buf_elems, reinterpret_cast<const __half*>(h_in),
+        reinterpret_cast<const __half*>(weight), reinterpret_cast<__half*>(h_out), reinterpret_cast<__half*>(y), hidden, eps,
+        ws->status);
+    SBVR_CUDA_TRY(cudaGetLastError());
+    return SBVR_OK;
+}

@@ -181,6 +181,7 @@ class SBVRLlamaForCausalLM(torch.nn.Module):
         self._bufs = {}
         self._graph = None
         self._stream = None
+        self._comm = None
 
     # ------------------------------------------------------------------ weights
     @torch.inference_mode()
@@ -220,6 +221,21 @@ class SBVRLlamaForCausalLM(torch.nn.Module):
         self.lm_head = _make_linear(parallel.shard_rows(head, r, n), G, dev)
         self._alloc_cache()
         return self
+
+    def enable_fused_allreduce(self, max_rows: int = 16) -> bool:
+        """Tensor parallel only: route the all-reduces of up to `max_rows` activation rows through the fused
+        peer-memory kernel.  Returns False (and keeps NCCL) when symmetric memory cannot be set up here."""
+        if self.tp_size == 1 and self.tp_group is None:
+            return False
+        from .comm import SymmetricAllReduce
+        try:
+            self._comm = SymmetricAllReduce(self.tp_group, self.device, max_rows, self.config.hidden_size,
+                                            2 * self.config.num_hidden_layers)
+        except Exception as e:                     # no peer mapping on this machine: NCCL stays
+            self._comm_error = repr(e)
+            self._comm = None
+        self._graph = None
+        return self._comm is not None
 
     def _alloc_cache(self):
         c = self.config
@@ -281,11 +297,17 @@ class SBVRLlamaForCausalLM(torch.nn.Module):
         nsplit = self._nsplit(T)
         ck = _lib.check
         ck(L.sbvr_embedding_f16(b.ids.data_ptr(), self.embed_tokens.data_ptr(), b.h.data_ptr(), T, H, st), "embedding")
-        delta = None
+        # Tensor parallel with few rows: the partial outputs of o and down go to symmetric memory and one fused
+        # kernel all-reduces them, adds the residual and applies the next RMSNorm.  Otherwise NCCL + add_rmsnorm.
+        comm = self._comm if (self._comm is not None and T <= self._comm.max_rows) else None
+        ws = _lib.workspace(self.device.index or 0, st) if comm is not None else None
+        n_layers = len(self.layers)
+        delta, normed = None, False
         for li, layer in enumerate(self.layers):
-            ck(L.sbvr_add_rmsnorm_f16(b.h.data_ptr(), None if delta is None else delta.data_ptr(),
-                                      layer.input_layernorm_weight.data_ptr(), b.h.data_ptr(), b.xn.data_ptr(), T, H,
-                                      eps, st), "rmsnorm")
+            if not normed:
+                ck(L.sbvr_add_rmsnorm_f16(b.h.data_ptr(), None if delta is None else delta.data_ptr(),
+                                          layer.input_layernorm_weight.data_ptr(), b.h.data_ptr(), b.xn.data_ptr(), T, H,
+                                          eps, st), "rmsnorm")
             layer.qkv_proj(b.xn, out=b.qkv)
             ck(L.sbvr_rope_append_f16(b.qkv.data_ptr(), b.positions.data_ptr(), self.inv_freq.data_ptr(),
                                       float(self.attention_scaling), self.kcache[li].data_ptr(),
@@ -295,17 +317,30 @@ class SBVRLlamaForCausalLM(torch.nn.Module):
                                     b.positions.data_ptr(), b.ao.data_ptr(),
                                     None if b.att_scratch is None else b.att_scratch.data_ptr(), T, tokens_per_seq,
                                     self.n_heads, self.n_kv, c.head_dim, self.max_ctx, scale, nsplit, st), "attention")
-            layer.o_proj(b.ao, out=b.o)
-            self._all_reduce(b.o)
-            ck(L.sbvr_add_rmsnorm_f16(b.h.data_ptr(), b.o.data_ptr(), layer.post_attention_layernorm_weight.data_ptr(),
-                                      b.h.data_ptr(), b.xn.data_ptr(), T, H, eps, st), "rmsnorm")
+            if comm is not None:
+                layer.o_proj(b.ao, out=comm.partial_out(2 * li, T))
+                comm.reduce_add_rmsnorm(2 * li, b.h, layer.post_attention_layernorm_weight, b.xn, T, eps, ws, st)
+            else:
+                layer.o_proj(b.ao, out=b.o)
+                self._all_reduce(b.o)
+                ck(L.sbvr_add_rmsnorm_f16(b.h.data_ptr(), b.o.data_ptr(), layer.post_attention_layernorm_weight.data_ptr(),
+                                          b.h.data_ptr(), b.xn.data_ptr(), T, H, eps, st), "rmsnorm")
             layer.gate_up_proj(b.xn, out=b.gu)
             ck(L.sbvr_silu_mul_f16(b.gu.data_ptr(), b.act.data_ptr(), T, self.inter, st), "silu_mul")
-            layer.down_proj(b.act, out=b.down)
-            self._all_reduce(b.down)
-            delta = b.down
-        ck(L.sbvr_add_rmsnorm_f16(b.h.data_ptr(), None if delta is None else delta.data_ptr(), self.norm_weight.data_ptr(),
-                                  None, b.xn.data_ptr(), T, H, eps, st), "rmsnorm")
+            if comm is not None:
+                layer.down_proj(b.act, out=comm.partial_out(2 * li + 1, T))
+                nw = self.layers[li + 1].input_layernorm_weight if li + 1 < n_layers else self.norm_weight
+                comm.reduce_add_rmsnorm(2 * li + 1, b.h, nw, b.xn, T, eps, ws, st)
+                delta, normed = None, True
+            else:
+                layer.down_proj(b.act, out=b.down)
+                self._all_reduce(b.down)
+                delta, normed = b.down, False
+        if not normed:
+            ck(L.sbvr_add_rmsnorm_f16(b.h.data_ptr(), None if delta is None else delta.data_ptr(),
+                                      self.norm_weight.data_ptr(), None, b.xn.data_ptr(), T, H, eps, st), "rmsnorm")
+        if self._comm is not None:
+            self._comm.end_step()
         if last_only and tokens_per_seq > 1:
             rows = b.xn.view(-1, tokens_per_seq, H)[:, -1, :].contiguous()
         else:

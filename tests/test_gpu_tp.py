@@ -32,6 +32,17 @@ def _worker(rank, world, port, q):
         a = tp.generate(ids, 10, use_graph=False)
         b = tp.generate(ids, 10, use_graph=True)
         same = bool(torch.equal(a, b))
+        # the same decode through the fused peer-memory all-reduce (symmetric memory), eager and captured
+        fused = tp.enable_fused_allreduce(16)
+        if fused:
+            c = tp.generate(ids, 10, use_graph=False)
+            d = tp.generate(ids, 10, use_graph=True)
+            same = same and bool(torch.equal(c, d)) and (c == a).float().mean().item() >= 0.8
+        else:
+            print("fused all-reduce unavailable:", getattr(tp, "_comm_error", "?"), flush=True)
+        fused_required = os.environ.get("SBVR_REQUIRE_FUSED_ALLREDUCE", "0") == "1"
+        if fused_required and not fused:
+            raise RuntimeError("symmetric memory set-up failed: " + getattr(tp, "_comm_error", "?"))
         err = -1.0
         if rank == 0:
             one = SBVRLlamaForCausalLM(cfg, device=dev, max_batch=2, max_ctx=64).init_synthetic(3)
