@@ -343,24 +343,37 @@ def llama_decode(torch, dev, dist, world, preset, batch, prompt, new_tokens):
     e1.record()
     torch.cuda.synchronize()
     prefill_ms = e0.elapsed_time(e1)
-    m.generate(ids, 4)                                 # captures the decode graph
-    b = m._act(batch, batch)
-    with torch.inference_mode():
-        b.ids.copy_(nxt)
-        b.positions.fill_(prompt)
-    torch.cuda.synchronize()
+    def timed_decode():
+        m.generate(ids, 4)                             # captures the decode graph
+        b = m._act(batch, batch)
+        with torch.inference_mode():
+            b.ids.copy_(nxt)
+            b.positions.fill_(prompt)
+        torch.cuda.synchronize()
+        if dist:
+            dist.barrier()
+        e0.record()
+        for _ in range(new_tokens):
+            m._graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        t_ms = e0.elapsed_time(e1)
+        if dist:
+            t = torch.tensor([t_ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            t_ms = float(t[0].item())
+        return t_ms
+    ms = timed_decode()
+    nccl_ms, exchange = None, "none (single GPU)"
     if dist:
-        dist.barrier()
-    e0.record()
-    for _ in range(new_tokens):
-        m._graph.replay()
-    e1.record()
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1)
-    if dist:
-        t = torch.tensor([ms, prefill_ms], device=dev)
+        exchange = "NCCL all-reduce"
+        if m.enable_fused_allreduce(16):               # same decode with the fused peer-memory all-reduce kernel
+            nccl_ms = ms
+            ms = timed_decode()
+            exchange = "fused one-shot all-reduce + add + RMSNorm over symmetric memory"
+        t = torch.tensor([prefill_ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, prefill_ms = float(t[0].item()), float(t[1].item())
+        prefill_ms = float(t[0].item())
     m._check()
     wbytes = m.packed_weight_bytes()
     peak, _ = measured_peak()
@@ -368,7 +381,9 @@ def llama_decode(torch, dev, dist, world, preset, batch, prompt, new_tokens):
            "tokens_per_s": round(batch * new_tokens / ms * 1e3, 1), "ms_per_step": round(ms / new_tokens, 4),
            "prefill_ms": round(prefill_ms, 2), "packed_weight_bytes_per_gpu": wbytes,
            "weight_stream_GBps_per_gpu": round(wbytes / (ms / new_tokens) / 1e6, 1),
-           "frac_of_hbm_roofline": round(wbytes / (ms / new_tokens) / 1e6 / peak, 4)}
+           "frac_of_hbm_roofline": round(wbytes / (ms / new_tokens) / 1e6 / peak, 4), "exchange": exchange}
+    if nccl_ms is not None:
+        res["tokens_per_s_nccl"] = round(batch * new_tokens / nccl_ms * 1e3, 1)
     del m
     torch.cuda.empty_cache()
     return res
@@ -382,6 +397,7 @@ def cpu_baseline(reps=None):
     N, K = 4096, 4096
     p = O.make_packed(N, K, S, G=G, mode="u16", C=C, seed=7)
     x = np.random.default_rng(1).standard_normal((1, K)).astype(np.float16)
+    O.c_lib().sbvr_oracle_set_threads(os.cpu_count() or 1)      # torchrun exports OMP_NUM_THREADS=1
     threads = O.c_lib().sbvr_oracle_threads()
     O.linear_c(x, p["bvr"], p["coeff_idx"], p["coeff"], G=G)
     t0 = time.perf_counter()

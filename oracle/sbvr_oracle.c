@@ -92,6 +92,16 @@ static void init_table(void)
     table_ready = 1;
 }
 
+/* Sets the number of OpenMP threads the checker uses (launchers such as torchrun export OMP_NUM_THREADS=1). */
+void sbvr_oracle_set_threads(int n)
+{
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int sbvr_oracle_threads(void)
 {
 #ifdef _OPENMP
