@@ -157,8 +157,9 @@ SBVR_API int sbvr_silu_mul_f16(const void* gate_up, void* out, int rows, int int
 SBVR_API int sbvr_embedding_f16(const int* ids, const void* table, void* out, int tokens, int hidden,
                                 sbvr_stream_t stream);
 
-/* out[row] = index of the first maximum of logits[row][0 .. vocab-1] (greedy decoding; torch.argmax's tie rule). */
-SBVR_API int sbvr_argmax_f16(const void* logits, int* out, int rows, int vocab, sbvr_stream_t stream);
+/* out[row] = index of the first maximum of logits[row][0 .. vocab-1] (greedy decoding; torch.argmax's tie rule).
+ * `scratch` (128 floats + 128 ints, may be NULL) lets few rows of a large vocabulary be scanned by many SMs. */
+SBVR_API int sbvr_argmax_f16(const void* logits, int* out, float* scratch, int rows, int vocab, sbvr_stream_t stream);
 
 /* ---- tensor parallel: one-shot all-reduce fused with the residual add and the RMSNorm ----------------------
  * delta = fp16(sum over ranks of partial_r) (fp32, rank order), h_out = h_in + delta, y = RMSNorm(h_out) * weight,

@@ -44,6 +44,8 @@ __global__ void __launch_bounds__(256) allreduce_add_rmsnorm_kernel(
     unsigned int* status) {
     __shared__ float red[8];
     __shared__ int ok_s;
+    pdl_launch_dependents();
+    pdl_wait();                                    // the partial of this rank (previous kernel) is complete from here on
     const unsigned int epoch = (unsigned int)(*step_ptr) * (unsigned int)calls_per_step + (unsigned int)call_idx + 1u;
     const size_t parity_off = (size_t)(call_idx & 1) * buf_elems;
     if (blockIdx.x == 0 && threadIdx.x < world) {
@@ -137,11 +139,11 @@ extern "C" int sbvr_allreduce_add_rmsnorm_f16(const void* peer_bufs_dev, const v
     if ((reinterpret_cast<uintptr_t>(h_in) | reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(h_out) |
          reinterpret_cast<uintptr_t>(y)) & 15)
         return SBVR_ERR_ALIGN;
-    allreduce_add_rmsnorm_kernel<<<rows, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-        reinterpret_cast<const unsigned long long*>(peer_bufs_dev), reinterpret_cast<const unsigned long long*>(peer_flags_dev),
-        step_dev, calls_per_step, call_idx, rank, world, buf_elems, reinterpret_cast<const __half*>(h_in),
-        reinterpret_cast<const __half*>(weight), reinterpret_cast<__half*>(h_out), reinterpret_cast<__half*>(y), hidden, eps,
-        ws->status);
-    SBVR_CUDA_TRY(cudaGetLastError());
+    SBVR_CUDA_TRY(launch_pdl(allreduce_add_rmsnorm_kernel, dim3(rows), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
+                             reinterpret_cast<const unsigned long long*>(peer_bufs_dev),
+                             reinterpret_cast<const unsigned long long*>(peer_flags_dev), step_dev, calls_per_step, call_idx,
+                             rank, world, buf_elems, reinterpret_cast<const __half*>(h_in),
+                             reinterpret_cast<const __half*>(weight), reinterpret_cast<__half*>(h_out),
+                             reinterpret_cast<__half*>(y), hidden, eps, ws->status));
     return SBVR_OK;
 }

@@ -1,5 +1,6 @@
 // C ABI of sbvr_b200: argument validation, workspace management and dispatch.  Nothing here
 // computes; see decode.cu, linear_simt.cu, linear_tc.cu.
+#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -7,6 +8,14 @@
 namespace sbvr {
 
 thread_local int g_last_cuda_error = 0;
+
+bool pdl_enabled() {
+    static const bool on = [] {
+        const char* e = getenv("SBVR_NO_PDL");
+        return !(e && e[0] == '1');
+    }();
+    return on;
+}
 
 int device_info(int device, DeviceInfo* out) {
     static std::mutex mu;

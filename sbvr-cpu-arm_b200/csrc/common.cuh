@@ -62,6 +62,22 @@ struct sbvr_workspace {
 
 namespace sbvr {
 
+// Launch with programmatic stream serialization: the grid may be scheduled while its predecessor on the stream is
+// still running; every such kernel executes griddepcontrol.wait before it touches what the predecessor produced.
+// SBVR_NO_PDL=1 in the environment turns the attribute off (plain stream order).
+bool pdl_enabled();
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 int launch_decode(const PackedW& w, __half* W, int ldw, int Kout, cudaStream_t st);
 int launch_linear_simt(const __half* x, const PackedW& w, const __half* bias, __half* y, int M, cudaStream_t st);
 bool linear_tc_supported(const PackedW& w, int M);

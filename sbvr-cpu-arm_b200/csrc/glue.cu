@@ -23,6 +23,8 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(const __half* h_in, co
                                                           const __half* __restrict__ weight, __half* h_out,
                                                           __half* __restrict__ y, int hidden, float eps) {
     __shared__ float red[8];
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t row = (size_t)blockIdx.x * hidden;
     const int nvec = hidden / 8;
     float ss = 0.0f;
@@ -81,16 +83,24 @@ __global__ void __launch_bounds__(256) rope_append_kernel(__half* __restrict__ q
                                                           const float* __restrict__ inv_freq, float attn_scaling,
                                                           __half* __restrict__ kcache, __half* __restrict__ vcache,
                                                           int tokens_per_seq, int n_heads, int n_kv, int d, int max_ctx) {
+    __shared__ __half cs_s[2][256];                // cos, sin of this token's position for i < head_dim / 2 <= 256
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     const int pos = positions[t];
     const int seq = t / tokens_per_seq;
     const int half_d = d / 2;
     __half* row = qkv + (size_t)t * (n_heads + 2 * n_kv) * d;
+    for (int i = threadIdx.x; i < half_d; i += blockDim.x) {       // the accurate cosf / sinf are the expensive part
+        const float ang = (float)pos * inv_freq[i];
+        cs_s[0][i] = __float2half_rn(cosf(ang) * attn_scaling);
+        cs_s[1][i] = __float2half_rn(sinf(ang) * attn_scaling);
+    }
+    __syncthreads();
     const int rot_items = (n_heads + n_kv) * half_d;
     for (int it = threadIdx.x; it < rot_items; it += blockDim.x) {
         const int head = it / half_d, i = it - head * half_d;
-        const float ang = (float)pos * inv_freq[i];
-        const __half c = __float2half_rn(cosf(ang) * attn_scaling), s = __float2half_rn(sinf(ang) * attn_scaling);
+        const __half c = cs_s[0][i], s = cs_s[1][i];
         __half* hp = row + (size_t)head * d;
         const __half x1 = hp[i], x2 = hp[i + half_d];
         const __half o1 = __hadd(__hmul(x1, c), __hmul(__hneg(x2), s));
@@ -126,6 +136,8 @@ __global__ void __launch_bounds__(128) attention_kernel(const __half* __restrict
     __shared__ float qs[R][AT_D];
     __shared__ float wm[4][R], wl[4][R];
     __shared__ float wacc[4][R][AT_D];
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x / n_kv, kvh = blockIdx.x - t * n_kv;
     const int split = blockIdx.y;
     const int seq = t / tokens_per_seq;
@@ -146,9 +158,13 @@ __global__ void __launch_bounds__(128) attention_kernel(const __half* __restrict
 #pragma unroll
         for (int e = 0; e < 4; ++e) acc[r][e] = 0.0f;
     }
-    // a warp takes 32 consecutive positions at a time: lane <-> position for the scores, lane <-> 4 dims for P.V
-    for (int base = p0 + warp * 32; base < p1; base += 128) {
+    // The CTA's positions are cut into four contiguous quarters, one per warp; a warp takes up to 32 consecutive
+    // positions at a time: lane <-> position for the scores, lane <-> 4 dims for P.V.
+    const int quarter = (p1 - p0 + 3) / 4;
+    const int w0 = min(p1, p0 + warp * quarter), w1 = min(p1, w0 + quarter);
+    for (int base = w0; base < w1; base += 32) {
         const int p = base + lane;
+        const int p1 = w1;                         // this warp's end (shadows the CTA's)
         float sc[R];
 #pragma unroll
         for (int r = 0; r < R; ++r) sc[r] = 0.0f;
@@ -185,14 +201,20 @@ __global__ void __launch_bounds__(128) attention_kernel(const __half* __restrict
             m[r] = nm;
         }
         const int np = min(32, p1 - base);
-        for (int j = 0; j < np; ++j) {
-            const uint2 vv = __ldg(reinterpret_cast<const uint2*>(vb + (size_t)(base + j) * AT_D) + lane);
-            const __half2* vh = reinterpret_cast<const __half2*>(&vv);
-            const float2 f0 = __half22float2(vh[0]), f1 = __half22float2(vh[1]);
+        for (int j0 = 0; j0 < np; j0 += 8) {       // eight V rows in flight; rows past the end carry weight 0
+            uint2 vv[8];
 #pragma unroll
-            for (int r = 0; r < R; ++r) {
-                const float wj = __shfl_sync(0xffffffffu, w[r], j);
-                acc[r][0] += wj * f0.x, acc[r][1] += wj * f0.y, acc[r][2] += wj * f1.x, acc[r][3] += wj * f1.y;
+            for (int u = 0; u < 8; ++u)
+                vv[u] = __ldg(reinterpret_cast<const uint2*>(vb + (size_t)min(base + j0 + u, max_ctx - 1) * AT_D) + lane);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const __half2* vh = reinterpret_cast<const __half2*>(&vv[u]);
+                const float2 f0 = __half22float2(vh[0]), f1 = __half22float2(vh[1]);
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    const float wj = __shfl_sync(0xffffffffu, w[r], j0 + u);
+                    acc[r][0] += wj * f0.x, acc[r][1] += wj * f0.y, acc[r][2] += wj * f1.x, acc[r][3] += wj * f1.y;
+                }
             }
         }
     }
@@ -230,6 +252,8 @@ __global__ void __launch_bounds__(128) attention_kernel(const __half* __restrict
 // merges the splits of one (token, head)                                   grid tokens * n_heads, 128 threads
 __global__ void __launch_bounds__(128) attention_combine_kernel(const float* __restrict__ part, __half* __restrict__ out,
                                                                 int nsplit) {
+    pdl_launch_dependents();
+    pdl_wait();
     const float* pp = part + (size_t)blockIdx.x * nsplit * (AT_D + 2);
     float gm = -INFINITY;
     for (int s = 0; s < nsplit; ++s) gm = fmaxf(gm, pp[(size_t)s * (AT_D + 2)]);
@@ -247,6 +271,8 @@ __global__ void __launch_bounds__(128) attention_combine_kernel(const float* __r
 // out[t, i] = fp16(silu(gate[t, i])) * up[t, i];   gu row = [gate (inter) | up (inter)]
 // ---------------------------------------------------------------------------------------------
 __global__ void silu_mul_kernel(const __half* __restrict__ gu, __half* __restrict__ out, int rows, int inter) {
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t nvec = (size_t)rows * inter / 8;
     for (size_t v = (size_t)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += (size_t)gridDim.x * blockDim.x) {
         const size_t e0 = v * 8;
@@ -269,19 +295,29 @@ __global__ void silu_mul_kernel(const __half* __restrict__ gu, __half* __restric
 
 __global__ void embedding_kernel(const int* __restrict__ ids, const __half* __restrict__ table, __half* __restrict__ out,
                                  int hidden) {
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t src = (size_t)ids[blockIdx.x] * hidden, dst = (size_t)blockIdx.x * hidden;
     for (int i = threadIdx.x; i < hidden / 8; i += blockDim.x)
         *reinterpret_cast<uint4*>(out + dst + (size_t)i * 8) = *reinterpret_cast<const uint4*>(table + src + (size_t)i * 8);
 }
 
-// index of the first maximum of each row (torch.argmax's tie rule); NaN wins like in torch       one CTA per row
-__global__ void __launch_bounds__(1024) argmax_kernel(const __half* __restrict__ logits, int* __restrict__ out, int vocab) {
+// index of the first maximum of each row (torch.argmax's tie rule); NaN wins like in torch.
+// grid (rows, parts): part `blockIdx.y` scans its slice of the row and leaves (value, index) in `partial`
+// (or, with one part, writes the result); argmax_final_kernel picks the winner of the parts.
+__global__ void __launch_bounds__(1024) argmax_kernel(const __half* __restrict__ logits, int* __restrict__ out, int vocab,
+                                                      float* __restrict__ pval, int* __restrict__ pidx) {
     __shared__ float bv[32];
     __shared__ int bi[32];
+    pdl_launch_dependents();
+    pdl_wait();
     const __half* row = logits + (size_t)blockIdx.x * vocab;
+    const int parts = (int)gridDim.y;
+    const int per = (vocab + parts - 1) / parts;
+    const int i0 = (int)blockIdx.y * per, i1 = min(vocab, i0 + per);
     float best = -INFINITY;
     int idx = 0x7fffffff;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+    for (int i = i0 + (int)threadIdx.x; i < i1; i += blockDim.x) {
         float v = __half2float(row[i]);
         if (v != v) v = INFINITY;
         if (v > best || (v == best && i < idx)) best = v, idx = i;
@@ -303,8 +339,35 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const __half* __restrict__
             const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
             if (ov > best || (ov == best && oi < idx)) best = ov, idx = oi;
         }
-        if (threadIdx.x == 0) out[blockIdx.x] = idx;
+        if (threadIdx.x == 0) {
+            if (parts == 1) {
+                out[blockIdx.x] = idx;
+            } else {
+                pval[(size_t)blockIdx.x * parts + blockIdx.y] = best;
+                pidx[(size_t)blockIdx.x * parts + blockIdx.y] = idx;
+            }
+        }
     }
+}
+
+__global__ void __launch_bounds__(32) argmax_final_kernel(const float* __restrict__ pval, const int* __restrict__ pidx,
+                                                          int* __restrict__ out, int parts) {
+    pdl_launch_dependents();
+    pdl_wait();
+    float best = -INFINITY;
+    int idx = 0x7fffffff;
+    for (int i = threadIdx.x; i < parts; i += 32) {
+        const float v = pval[(size_t)blockIdx.x * parts + i];
+        const int j = pidx[(size_t)blockIdx.x * parts + i];
+        if (v > best || (v == best && j < idx)) best = v, idx = j;
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (ov > best || (ov == best && oi < idx)) best = ov, idx = oi;
+    }
+    if (threadIdx.x == 0) out[blockIdx.x] = idx;
 }
 
 }  // namespace sbvr
@@ -320,10 +383,10 @@ int sbvr_add_rmsnorm_f16(const void* h_in, const void* delta, const void* weight
     if ((reinterpret_cast<uintptr_t>(h_in) | reinterpret_cast<uintptr_t>(delta) | reinterpret_cast<uintptr_t>(weight) |
          reinterpret_cast<uintptr_t>(h_out) | reinterpret_cast<uintptr_t>(y)) & 15)
         return SBVR_ERR_ALIGN;
-    add_rmsnorm_kernel<<<rows, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-        reinterpret_cast<const __half*>(h_in), reinterpret_cast<const __half*>(delta),
-        reinterpret_cast<const __half*>(weight), reinterpret_cast<__half*>(h_out), reinterpret_cast<__half*>(y), hidden, eps);
-    SBVR_CUDA_TRY(cudaGetLastError());
+    SBVR_CUDA_TRY(launch_pdl(add_rmsnorm_kernel, dim3(rows), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
+                             reinterpret_cast<const __half*>(h_in), reinterpret_cast<const __half*>(delta),
+                             reinterpret_cast<const __half*>(weight), reinterpret_cast<__half*>(h_out),
+                             reinterpret_cast<__half*>(y), hidden, eps));
     return SBVR_OK;
 }
 
@@ -334,10 +397,10 @@ int sbvr_rope_append_f16(void* qkv, const int* positions, const float* inv_freq,
     if (tokens < 1 || tokens_per_seq < 1 || tokens % tokens_per_seq || n_heads < 1 || n_kv < 1 || head_dim < 2 ||
         head_dim % 2 || max_ctx < 1)
         return SBVR_ERR_BAD_ARG;
-    rope_append_kernel<<<tokens, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-        reinterpret_cast<__half*>(qkv), positions, inv_freq, attn_scaling, reinterpret_cast<__half*>(kcache),
-        reinterpret_cast<__half*>(vcache), tokens_per_seq, n_heads, n_kv, head_dim, max_ctx);
-    SBVR_CUDA_TRY(cudaGetLastError());
+    SBVR_CUDA_TRY(launch_pdl(rope_append_kernel, dim3(tokens), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
+                             reinterpret_cast<__half*>(qkv), positions, inv_freq, attn_scaling,
+                             reinterpret_cast<__half*>(kcache), reinterpret_cast<__half*>(vcache), tokens_per_seq, n_heads,
+                             n_kv, head_dim, max_ctx));
     return SBVR_OK;
 }
 
@@ -358,9 +421,9 @@ int sbvr_attention_f16(const void* qkv, const void* kcache, const void* vcache, 
     const __half* kc = reinterpret_cast<const __half*>(kcache);
     const __half* vc = reinterpret_cast<const __half*>(vcache);
     __half* o = reinterpret_cast<__half*>(out);
-#define SBVR_ATT(RR)                                                                                             \
-    attention_kernel<RR><<<grid, 128, 0, st>>>(q, kc, vc, positions, o, scratch, tokens_per_seq, n_heads, n_kv, \
-                                                max_ctx, scale, nsplit)
+#define SBVR_ATT(RR)                                                                                              \
+    SBVR_CUDA_TRY(launch_pdl(attention_kernel<RR>, grid, dim3(128), 0, st, q, kc, vc, positions, o, scratch,     \
+                             tokens_per_seq, n_heads, n_kv, max_ctx, scale, nsplit))
     switch (R) {
         case 1: SBVR_ATT(1); break;
         case 2: SBVR_ATT(2); break;
@@ -369,11 +432,9 @@ int sbvr_attention_f16(const void* qkv, const void* kcache, const void* vcache, 
         default: return SBVR_ERR_UNSUPPORTED;
     }
 #undef SBVR_ATT
-    SBVR_CUDA_TRY(cudaGetLastError());
-    if (nsplit > 1) {
-        attention_combine_kernel<<<tokens * n_heads, 128, 0, st>>>(scratch, o, nsplit);
-        SBVR_CUDA_TRY(cudaGetLastError());
-    }
+    if (nsplit > 1)
+        SBVR_CUDA_TRY(launch_pdl(attention_combine_kernel, dim3(tokens * n_heads), dim3(128), 0, st,
+                                 static_cast<const float*>(scratch), o, nsplit));
     return SBVR_OK;
 }
 
@@ -383,9 +444,8 @@ int sbvr_silu_mul_f16(const void* gate_up, void* out, int rows, int inter, sbvr_
     if ((reinterpret_cast<uintptr_t>(gate_up) | reinterpret_cast<uintptr_t>(out)) & 15) return SBVR_ERR_ALIGN;
     const size_t nvec = (size_t)rows * inter / 8;
     const int blocks = (int)((nvec + 255) / 256 < 4096 ? (nvec + 255) / 256 : 4096);
-    silu_mul_kernel<<<blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(reinterpret_cast<const __half*>(gate_up),
-                                                                              reinterpret_cast<__half*>(out), rows, inter);
-    SBVR_CUDA_TRY(cudaGetLastError());
+    SBVR_CUDA_TRY(launch_pdl(silu_mul_kernel, dim3(blocks), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
+                             reinterpret_cast<const __half*>(gate_up), reinterpret_cast<__half*>(out), rows, inter));
     return SBVR_OK;
 }
 
@@ -393,17 +453,28 @@ int sbvr_embedding_f16(const int* ids, const void* table, void* out, int tokens,
     if (!ids || !table || !out || tokens < 1 || hidden < 8) return SBVR_ERR_BAD_ARG;
     if (hidden % 8) return SBVR_ERR_SHAPE;
     if ((reinterpret_cast<uintptr_t>(table) | reinterpret_cast<uintptr_t>(out)) & 15) return SBVR_ERR_ALIGN;
-    embedding_kernel<<<tokens, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(ids, reinterpret_cast<const __half*>(table),
-                                                                               reinterpret_cast<__half*>(out), hidden);
-    SBVR_CUDA_TRY(cudaGetLastError());
+    SBVR_CUDA_TRY(launch_pdl(embedding_kernel, dim3(tokens), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream), ids,
+                             reinterpret_cast<const __half*>(table), reinterpret_cast<__half*>(out), hidden));
     return SBVR_OK;
 }
 
-int sbvr_argmax_f16(const void* logits, int* out, int rows, int vocab, sbvr_stream_t stream) {
+int sbvr_argmax_f16(const void* logits, int* out, float* scratch, int rows, int vocab, sbvr_stream_t stream) {
     if (!logits || !out || rows < 1 || vocab < 1) return SBVR_ERR_BAD_ARG;
-    argmax_kernel<<<rows, 1024, 0, reinterpret_cast<cudaStream_t>(stream)>>>(reinterpret_cast<const __half*>(logits), out,
-                                                                           vocab);
-    SBVR_CUDA_TRY(cudaGetLastError());
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    // few rows of a large vocabulary: cut every row into up to 64 parts so that more than one SM scans it
+    int parts = 1;
+    if (scratch && vocab >= 16384) {
+        parts = 128 / rows;
+        if (parts > 64) parts = 64;
+        if (parts < 1) parts = 1;
+    }
+    float* pval = scratch;
+    int* pidx = reinterpret_cast<int*>(scratch) + (size_t)rows * parts;
+    SBVR_CUDA_TRY(launch_pdl(argmax_kernel, dim3((unsigned)rows, (unsigned)parts), dim3(1024), 0, st,
+                             reinterpret_cast<const __half*>(logits), out, vocab, pval, pidx));
+    if (parts > 1)
+        SBVR_CUDA_TRY(launch_pdl(argmax_final_kernel, dim3(rows), dim3(32), 0, st, static_cast<const float*>(pval),
+                                 static_cast<const int*>(pidx), out, parts));
     return SBVR_OK;
 }
 

@@ -110,6 +110,8 @@ __device__ __forceinline__ void gm_ld32(uint32_t taddr, float (&d)[32]) {
 // of 64-k stage kst; position p of a stage is k = 64 kst + 32 (p / 32) + (p % 32) / 2 + 16 (p & 1).
 __global__ void gemm_retile_x_kernel(const __half* __restrict__ x, __half* __restrict__ xt, int M, int K, int NX,
                                      int MT) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int KST = K / 64;
     const size_t chunks = (size_t)MT * KST * NX * 8;
     for (size_t c = (size_t)blockIdx.x * blockDim.x + threadIdx.x; c < chunks; c += (size_t)gridDim.x * blockDim.x) {
@@ -150,6 +152,8 @@ __global__ void __launch_bounds__(GM_THREADS, 1) linear_gemm_kernel(const GmPara
     unsigned char* xs = smem + GM_HDR;                           // [GM_XSTAGES][STAGE_BYTES]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    pdl_launch_dependents();
+    pdl_wait();                                    // the re-tiled activations come from the previous kernel
     if (threadIdx.x == 0) {
         for (int i = 0; i < GM_XSTAGES; ++i) {
             mbar_init(&x_full[i], 1);
@@ -538,8 +542,7 @@ static int gm_launch_inst(const GmParams& p, int grid, int smem, cudaStream_t st
                                            227 * 1024));
         configured_for = dev;
     }
-    linear_gemm_kernel<S, NX><<<grid, GM_THREADS, smem, st>>>(p);
-    SBVR_CUDA_TRY(cudaGetLastError());
+    SBVR_CUDA_TRY(launch_pdl(linear_gemm_kernel<S, NX>, dim3(grid), dim3(GM_THREADS), (size_t)smem, st, p));
     return SBVR_OK;
 }
 template <int S>
@@ -568,8 +571,7 @@ int launch_linear_gemm(const __half* x, const PackedW& w, const __half* bias, __
         const size_t chunks = (size_t)pl.MT * pl.NX * w.K / 8;
         const int blocks = (int)((chunks + 255) / 256 < (size_t)di.sm_count * 8 ? (chunks + 255) / 256
                                                                                : (size_t)di.sm_count * 8);
-        gemm_retile_x_kernel<<<blocks, 256, 0, st>>>(x, xt, M, w.K, pl.NX, pl.MT);
-        SBVR_CUDA_TRY(cudaGetLastError());
+        SBVR_CUDA_TRY(launch_pdl(gemm_retile_x_kernel, dim3(blocks), dim3(256), 0, st, x, xt, M, w.K, pl.NX, pl.MT));
     }
     GmParams p;
     p.xt = xt, p.bvr = w.bvr, p.idx = w.idx, p.coeff = w.coeff, p.bias = bias, p.y = y;

@@ -168,6 +168,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) linear_tc_kernel(const TcParams
     int prof_tile = 0;
 #endif
     TC_PROF_MARK(0);
+    pdl_launch_dependents();                       // the next kernel on the stream may be scheduled as SMs free up
     extern __shared__ __align__(128) unsigned char smem[];
     constexpr int SP = tc_sp(S);
     constexpr int TN = tc_tn(S);
@@ -406,8 +407,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1) linear_tc_kernel(const TcParams
             ioff_l += wrap ? IWRAP_B : ISTEP_B;
             if (wrap) kb_l = my_lo;
         };
-        // ---- set-up shared by the CTA.  First the activations, copied as they are into the first half of each
-        // block's digit area (the oldest cp.async group), then the packed words of the first three tiles.
+        // ---- set-up shared by the CTA.  The packed words of the first three tiles are requested first: weights do
+        // not depend on the previous kernel of the stream, so this (like the barrier set-up, the codebook copy and
+        // the tensor-memory allocation) overlaps that kernel's tail.  The activations do: wait for it, then copy
+        // them as they are into the first half of each block's digit area.
+        load_tile();
+        TC_PROF_MARK(11);
+        load_tile();
+        load_tile();
+        pdl_wait();
         {
             const int nchunk = M * KB * 32;        // 16-byte pieces
             for (int c = ctid; c < nchunk; c += TC_CTHREADS) {
@@ -421,12 +429,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) linear_tc_kernel(const TcParams
             asm volatile("cp.async.commit_group;" ::: "memory");
         }
         TC_PROF_MARK(10);
-        load_tile();
-        TC_PROF_MARK(11);
-        load_tile();
-        load_tile();
         TC_PROF_MARK(5);
-        asm volatile("cp.async.wait_group 3;" ::: "memory");       // this thread's pieces of x have landed
+        asm volatile("cp.async.wait_group 0;" ::: "memory");       // this thread's pieces of x have landed
         named_bar_sync(2, TC_CTHREADS);                            // ... and everybody else's
         TC_PROF_MARK(6);
         {
@@ -778,8 +782,7 @@ static int tc_launch_inst(const TcParams& p, int grid, int smem, cudaStream_t st
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
         configured_for = dev;
     }
-    linear_tc_kernel<S, NSUB, M, IDXB><<<grid, TC_THREADS, smem, st>>>(p);
-    SBVR_CUDA_TRY(cudaGetLastError());
+    SBVR_CUDA_TRY(launch_pdl(linear_tc_kernel<S, NSUB, M, IDXB>, dim3(grid), dim3(TC_THREADS), (size_t)smem, st, p));
     return SBVR_OK;
 }
 template <int S, int NSUB, int M>

@@ -182,6 +182,7 @@ class SBVRLlamaForCausalLM(torch.nn.Module):
         self._graph = None
         self._stream = None
         self._comm = None
+        self._argmax_scratch = torch.empty(256, dtype=torch.float32, device=self.device)
 
     # ------------------------------------------------------------------ weights
     @torch.inference_mode()
@@ -279,7 +280,7 @@ class SBVRLlamaForCausalLM(torch.nn.Module):
     def _nsplit(self, tokens: int) -> int:
         # decode with few tokens: split the context so that about one CTA per SM works
         ctas = tokens * self.n_kv
-        return 1 if ctas >= 96 else max(1, min(16, 128 // ctas))
+        return 1 if ctas >= 96 else max(1, min(16, 192 // ctas))
 
     # ------------------------------------------------------------------ one forward over `tokens` rows
     def _all_reduce(self, t: torch.Tensor):
@@ -352,7 +353,8 @@ class SBVRLlamaForCausalLM(torch.nn.Module):
             full = g.permute(1, 0, 2).reshape(b.logits.shape[0], -1).contiguous()
         else:
             full = b.logits
-        ck(L.sbvr_argmax_f16(full.data_ptr(), b.next_ids.data_ptr(), full.shape[0], full.shape[1], st), "argmax")
+        ck(L.sbvr_argmax_f16(full.data_ptr(), b.next_ids.data_ptr(), self._argmax_scratch.data_ptr(), full.shape[0],
+                             full.shape[1], st), "argmax")
         return full
 
     # ------------------------------------------------------------------ public API

@@ -56,7 +56,7 @@ lib.sbvr_silu_mul_f16.argtypes = [_vp, _vp, _i, _i, _vp]
 lib.sbvr_silu_mul_f16.restype = _i
 lib.sbvr_embedding_f16.argtypes = [_vp, _vp, _vp, _i, _i, _vp]
 lib.sbvr_embedding_f16.restype = _i
-lib.sbvr_argmax_f16.argtypes = [_vp, _vp, _i, _i, _vp]
+lib.sbvr_argmax_f16.argtypes = [_vp, _vp, _vp, _i, _i, _vp]
 lib.sbvr_argmax_f16.restype = _i
 
 lib.sbvr_allreduce_add_rmsnorm_f16.argtypes = [_vp, _vp, _vp, _i, _i, _i, _i, _sz, _vp, _vp, _vp, _vp, _i, _i, _f, _vp, _vp]

@@ -111,7 +111,13 @@ def test_argmax_kernel_first_maximum():
     x[1, 777] = 100.0
     x[1, 90000] = 100.0
     out = torch.empty(3, dtype=torch.int32, device="cuda")
-    _lib.check(_lib.lib.sbvr_argmax_f16(x.data_ptr(), out.data_ptr(), 3, 128256, torch.cuda.current_stream().cuda_stream))
+    scratch = torch.empty(256, dtype=torch.float32, device="cuda")
+    _lib.check(_lib.lib.sbvr_argmax_f16(x.data_ptr(), out.data_ptr(), scratch.data_ptr(), 3, 128256,
+                                        torch.cuda.current_stream().cuda_stream))
+    out1 = torch.empty(3, dtype=torch.int32, device="cuda")
+    _lib.check(_lib.lib.sbvr_argmax_f16(x.data_ptr(), out1.data_ptr(), None, 3, 128256,
+                                        torch.cuda.current_stream().cuda_stream))
+    assert torch.equal(out, out1)
     assert out[1].item() == 777
     assert torch.equal(out.long(), x.float().argmax(-1))
 
