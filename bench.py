@@ -226,6 +226,7 @@ def run_ours(args):
         decodes = [llama_decode(torch, dev, dist, world, "8b", 1, 512, 256)]
         if not args.skip_70b:
             decodes.append(llama_decode(torch, dev, dist, world, "70b", 1, 1024, 256))
+            decodes.append(llama_decode(torch, dev, dist, world, "70b", 16, 1024, 64))
         extra["llama_decode"] = decodes
     for (d, s_), w in _lib._workspaces.items():
         assert w.status(s_) == 0, "a device-side wait timed out during the benchmark"

@@ -79,6 +79,28 @@ def test_decode_steps_match_full_forward(tiny):
     m._check()
 
 
+def test_batch_of_eight_uses_batched_linears():
+    """Eight sequences: every linear of a decode step has M = 8 (the tensor-core GEMM path), attention serves 8 x n_kv
+    query groups; the steps must still reproduce the full causal forward of the reference restatement."""
+    from models.sbvr_llama import LlamaConfig, SBVRLlamaForCausalLM
+    m = SBVRLlamaForCausalLM(LlamaConfig.preset("tiny"), max_batch=8, max_ctx=48).init_synthetic(5)
+    params = _ref_params(m)
+    gen = torch.Generator(device="cuda").manual_seed(8)
+    ids = torch.randint(0, m.config.vocab_size, (8, 20), device="cuda", generator=gen)
+    ref = llama_ref.forward(params, ids).float()
+    m.prefill(ids[:, :12])
+    for t in range(12, 20):
+        pos = torch.full((8,), t, dtype=torch.int32, device="cuda")
+        m.decode_step(ids[:, t], pos)
+        b = m._act(8, 8)
+        err = ((b.logits.float() - ref[:, t]).abs().max() / ref[:, t].abs().max()).item()
+        assert err <= TOL, (t, err)
+    a = m.generate(ids[:, :12], 6, use_graph=False)
+    g = m.generate(ids[:, :12], 6, use_graph=True)
+    assert torch.equal(a, g)
+    m._check()
+
+
 def test_generate_graph_equals_eager(tiny):
     m, _ = tiny
     ids = torch.randint(0, m.config.vocab_size, (2, 20), device="cuda", generator=torch.Generator(device="cuda").manual_seed(7))
@@ -141,3 +163,46 @@ def test_attention_kernel_against_softmax(ctx, nsplit):
     vv = llama_ref.repeat_kv(V[:, :, :ctx], nh // nkv).float()
     ref = (torch.softmax(q @ kk.transpose(2, 3) * d ** -0.5, -1) @ vv).reshape(B, nh * d)
     assert ((out.float() - ref).abs().max() / ref.abs().max()).item() < 5e-3
+
+
+def test_model_from_reference_style_directory(tmp_path):
+    """Per-projection files named as the reference's encoder names them (o_proj and lm_head left dense, as the
+    reference leaves them) -> SBVRLlamaForCausalLM without decoding anything -> logits of the restated reference."""
+    import sbvr
+    from models import loader
+    from models.sbvr_llama import LlamaConfig, SBVRLlamaForCausalLM
+    cfg = LlamaConfig.preset("tiny")
+    H, I = cfg.hidden_size, cfg.intermediate_size
+    qd, kvd = cfg.num_attention_heads * cfg.head_dim, cfg.num_key_value_heads * cfg.head_dim
+    shapes = {"q": (qd, H), "k": (kvd, H), "v": (kvd, H), "gate_proj": (I, H), "up_proj": (I, H), "down_proj": (H, I)}
+    g = torch.Generator().manual_seed(4)
+    dense = {"model.embed_tokens.weight": (torch.randn((cfg.vocab_size, H), generator=g) * 0.02).half(),
+             "model.norm.weight": (1 + 0.1 * torch.randn(H, generator=g)).half(),
+             "lm_head.weight": (torch.randn((cfg.vocab_size, H), generator=g) * 0.02).half()}
+    layers = []
+    for i in range(cfg.num_hidden_layers):
+        lw = {}
+        for name, (N, K) in shapes.items():
+            p = O.make_packed(N, K, 4, G=256, mode="u8", C=256, seed=100 * i + len(name))
+            w = sbvr.sbvr.from_packed(torch.from_numpy(p["bvr"].view(np.int32)), torch.from_numpy(p["coeff_idx"]),
+                                      torch.from_numpy(p["coeff"]), device=torch.device("cpu"))
+            w.save(str(tmp_path / f"layer_{i}_{name}.pt"))
+            lw[name.replace("_proj", "")] = torch.from_numpy(O.decode_c(p["bvr"], p["coeff_idx"], p["coeff"], G=256)).cuda()
+        Wo = (torch.randn((H, qd), generator=g) * 0.02).half()
+        dense[f"model.layers.{i}.self_attn.o_proj.weight"] = Wo
+        dense[f"model.layers.{i}.input_layernorm.weight"] = (1 + 0.1 * torch.randn(H, generator=g)).half()
+        dense[f"model.layers.{i}.post_attention_layernorm.weight"] = (1 + 0.1 * torch.randn(H, generator=g)).half()
+        lw.update({"o": Wo.cuda(), "input_norm": dense[f"model.layers.{i}.input_layernorm.weight"].cuda(),
+                   "post_norm": dense[f"model.layers.{i}.post_attention_layernorm.weight"].cuda()})
+        layers.append(lw)
+    m = SBVRLlamaForCausalLM(cfg, max_batch=2, max_ctx=64)
+    loader.load_directory(m, str(tmp_path), dense)
+    params = {"embed": dense["model.embed_tokens.weight"].cuda(), "layers": layers, "norm": dense["model.norm.weight"].cuda(),
+              "lm_head": dense["lm_head.weight"].cuda(), "n_heads": cfg.num_attention_heads,
+              "n_kv": cfg.num_key_value_heads, "head_dim": cfg.head_dim, "eps": cfg.rms_norm_eps, "theta": cfg.rope_theta}
+    ids = torch.randint(0, cfg.vocab_size, (2, 30), device="cuda", generator=torch.Generator(device="cuda").manual_seed(6))
+    logits = m(ids).float()
+    ref = llama_ref.forward(params, ids).float()
+    err = ((logits - ref).abs().max() / ref.abs().max()).item()
+    assert err <= TOL, err
+    assert torch.equal(m.generate(ids, 5, use_graph=True), m.generate(ids, 5, use_graph=False))
