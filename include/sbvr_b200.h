@@ -143,11 +143,19 @@ SBVR_API int sbvr_rope_append_f16(void* qkv, const int* positions, const float* 
 /* out[token][head][:] = softmax(q . K^T * scale) . V over cache positions 0 .. positions[token] of the token's
  * sequence, grouped-query (n_heads % n_kv == 0, ratio 1, 2, 4 or 8), head_dim 128.  Serves decode (one token per
  * sequence) and causal prefill (every token attends up to itself; its k, v must be in the cache already).
- * nsplit > 1 splits the positions over CTAs (decode at long context) and needs `scratch` of
- * tokens * n_heads * nsplit * 130 floats.  repeat_kv + eager_attention_forward (models/sbvr_llama.py:243-278). */
+ * nsplit > 1 splits the positions over CTAs (decode at long context); the split that finishes last merges them.  It
+ * needs `scratch` of tokens * n_heads * nsplit * 130 floats followed by tokens * n_kv 32-bit counters that are zero
+ * before the first call (every call leaves them zero).  repeat_kv + eager_attention_forward (models/sbvr_llama.py:243-278). */
 SBVR_API int sbvr_attention_f16(const void* qkv, const void* kcache, const void* vcache, const int* positions,
                                 void* out, float* scratch, int tokens, int tokens_per_seq, int n_heads, int n_kv,
                                 int head_dim, int max_ctx, float scale, int nsplit, sbvr_stream_t stream);
+
+/* Decode form of the two calls above in one launch: one new token per sequence; q and the token's k are rotated
+ * inside the attention kernel (qkv is left as it is), the rotated k and v are appended to the caches at
+ * positions[token] by the CTA that attends to that position.  Same scratch rules as sbvr_attention_f16. */
+SBVR_API int sbvr_rope_attention_f16(const void* qkv, const int* positions, const float* inv_freq, float attn_scaling,
+                                     void* kcache, void* vcache, void* out, float* scratch, int tokens, int n_heads,
+                                     int n_kv, int head_dim, int max_ctx, float scale, int nsplit, sbvr_stream_t stream);
 
 /* out[row][i] = fp16(silu(gate[row][i])) * up[row][i] with gate_up[row] = [gate (inter) | up (inter)]:
  * the activation of LlamaMLP.forward (models/sbvr_llama.py:238-240) on a fused gate/up linear.  inter % 8 == 0. */
@@ -160,6 +168,23 @@ SBVR_API int sbvr_embedding_f16(const int* ids, const void* table, void* out, in
 /* out[row] = index of the first maximum of logits[row][0 .. vocab-1] (greedy decoding; torch.argmax's tie rule).
  * `scratch` (128 floats + 128 ints, may be NULL) lets few rows of a large vocabulary be scanned by many SMs. */
 SBVR_API int sbvr_argmax_f16(const void* logits, int* out, float* scratch, int rows, int vocab, sbvr_stream_t stream);
+
+/* ---- decode linears with the preceding element-wise op folded in ---------------------------------------------
+ * The decode GEMV (algo 2 of sbvr_linear_f16: M <= 4, N % 32 == 0, K % 256 == 0) brings the whole activation row
+ * into every CTA anyway, so the op in front of the linear can be applied on the way in instead of in a launch of
+ * its own:
+ *   SBVR_XOP_SILU_MUL     x = fp16(silu(g)) * u, `x` pointing at rows [g (K) | u (K)] of pitch 2K
+ *                         (LlamaMLP.forward, models/sbvr_llama.py:238-240, in front of down_proj)
+ *   SBVR_XOP_ADD_RMSNORM  x = norm_weight * fp16((h + delta) * rsqrt(mean((h + delta)^2) + eps)) with h = `x`
+ *                         (pitch K), delta NULL = no add; h + delta is also stored to h_out (may be NULL; must be a
+ *                         buffer other than h) (LlamaDecoderLayer.forward :395-406 + LlamaRMSNorm.forward :118-123)
+ * Same rounding as sbvr_silu_mul_f16 / sbvr_add_rmsnorm_f16 followed by sbvr_linear_f16.  Returns
+ * SBVR_ERR_UNSUPPORTED where the decode GEMV does not apply (the caller then runs the separate kernels). */
+enum { SBVR_XOP_NONE = 0, SBVR_XOP_SILU_MUL = 1, SBVR_XOP_ADD_RMSNORM = 2 };
+SBVR_API int sbvr_linear_fused_f16(int x_op, const void* x, const void* delta, const void* norm_weight, void* h_out,
+                                   float eps, const uint32_t* bvr, const void* coeff_idx, int idx_bytes, const void* coeff,
+                                   int C, const void* bias, void* y, int M, int N, int K, int S, int G,
+                                   sbvr_workspace_t* ws, sbvr_stream_t stream);
 
 /* ---- tensor parallel: one-shot all-reduce fused with the residual add and the RMSNorm ----------------------
  * delta = fp16(sum over ranks of partial_r) (fp32, rank order), h_out = h_in + delta, y = RMSNorm(h_out) * weight,

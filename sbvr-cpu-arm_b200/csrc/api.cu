@@ -204,6 +204,29 @@ int sbvr_linear_f16(const void* x, const uint32_t* bvr, const void* coeff_idx, i
     return launch_linear_simt(xh, w, bh, yh, M, st);
 }
 
+int sbvr_linear_fused_f16(int x_op, const void* x, const void* delta, const void* norm_weight, void* h_out, float eps,
+                          const uint32_t* bvr, const void* coeff_idx, int idx_bytes, const void* coeff, int C,
+                          const void* bias, void* y, int M, int N, int K, int S, int G, sbvr_workspace_t* ws,
+                          sbvr_stream_t stream) {
+    PackedW w;
+    int rc = make_packed(&w, bvr, coeff_idx, idx_bytes, coeff, C, N, K, S, G);
+    if (rc) return rc;
+    if (!x || !y || M < 1) return SBVR_ERR_BAD_ARG;
+    if (x_op != SBVR_XOP_SILU_MUL && x_op != SBVR_XOP_ADD_RMSNORM) return SBVR_ERR_BAD_ARG;
+    if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(y) & 1)) return SBVR_ERR_ALIGN;
+    DeviceInfo di;
+    if (!ws) return SBVR_ERR_WORKSPACE;
+    rc = device_info(ws->device, &di);
+    if (rc) return rc;
+    if (di.cc_major != 10 || !linear_tc_supported(w, M)) return SBVR_ERR_UNSUPPORTED;
+    XOp xop;
+    xop.op = x_op;
+    xop.delta = reinterpret_cast<const __half*>(delta), xop.norm_w = reinterpret_cast<const __half*>(norm_weight);
+    xop.h_out = reinterpret_cast<__half*>(h_out), xop.eps = eps;
+    return launch_linear_tc(reinterpret_cast<const __half*>(x), w, reinterpret_cast<const __half*>(bias),
+                            reinterpret_cast<__half*>(y), M, ws, reinterpret_cast<cudaStream_t>(stream), &xop);
+}
+
 int sbvr_linear_f16_host(const void* x_host, const uint32_t* bvr, const void* coeff_idx, int idx_bytes,
                          const void* coeff, int C, const void* bias, void* y_host, int M, int N, int K, int S, int G,
                          int algo, sbvr_workspace_t* ws, sbvr_stream_t stream) {

@@ -81,8 +81,16 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
 int launch_decode(const PackedW& w, __half* W, int ldw, int Kout, cudaStream_t st);
 int launch_linear_simt(const __half* x, const PackedW& w, const __half* bias, __half* y, int M, cudaStream_t st);
 bool linear_tc_supported(const PackedW& w, int M);
+// What the decode GEMV makes its activations of while it brings them in.
+struct XOp {
+    int op;                  // SBVR_XOP_*
+    const __half* delta;     // ADD_RMSNORM: added to x first (may be NULL)
+    const __half* norm_w;    // ADD_RMSNORM: RMSNorm weight [K]
+    __half* h_out;           // ADD_RMSNORM: x + delta is stored here (may be NULL; must not be x)
+    float eps;
+};
 int launch_linear_tc(const __half* x, const PackedW& w, const __half* bias, __half* y, int M,
-                     sbvr_workspace* ws, cudaStream_t st);
+                     sbvr_workspace* ws, cudaStream_t st, const XOp* xop = nullptr);
 bool linear_gemm_supported(const PackedW& w, int M);
 size_t linear_gemm_workspace_bytes(const PackedW& w, int M, int sm_count);
 int launch_linear_gemm(const __half* x, const PackedW& w, const __half* bias, __half* y, int M,

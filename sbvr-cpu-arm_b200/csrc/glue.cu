@@ -128,28 +128,66 @@ __global__ void __launch_bounds__(256) rope_append_kernel(__half* __restrict__ q
 constexpr int AT_D = 128;
 constexpr int AT_RMAX = 8;
 
+// `inv_freq` != NULL (decode, one token per sequence): the rotary embedding is applied here -- q on its way into shared
+// memory; the token's own k by the CTA whose positions include it, which also appends k and v to the cache and
+// takes them from shared memory (the cache rows are read through the read-only path).
 template <int R>
-__global__ void __launch_bounds__(128) attention_kernel(const __half* __restrict__ qkv, const __half* __restrict__ kcache,
-                                                        const __half* __restrict__ vcache, const int* __restrict__ positions,
-                                                        __half* __restrict__ out, float* __restrict__ part, int tokens_per_seq,
-                                                        int n_heads, int n_kv, int max_ctx, float scale, int nsplit) {
+__global__ void __launch_bounds__(128) attention_kernel(const __half* __restrict__ qkv, __half* kcache, __half* vcache,
+                                                        const int* __restrict__ positions, __half* __restrict__ out,
+                                                        float* __restrict__ part, unsigned int* __restrict__ counters,
+                                                        int tokens_per_seq, int n_heads, int n_kv, int max_ctx, float scale,
+                                                        int nsplit, const float* __restrict__ inv_freq, float attn_scaling) {
     __shared__ float qs[R][AT_D];
     __shared__ float wm[4][R], wl[4][R];
     __shared__ float wacc[4][R][AT_D];
+    __shared__ __half cs_s[2][AT_D / 2];
+    __shared__ __align__(16) __half knew[AT_D], vnew[AT_D];
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x / n_kv, kvh = blockIdx.x - t * n_kv;
     const int split = blockIdx.y;
     const int seq = t / tokens_per_seq;
-    const int ctx = min(positions[t] + 1, max_ctx);
+    const int pos = positions[t];
+    const int ctx = min(pos + 1, max_ctx);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const __half* qrow = qkv + (size_t)t * (n_heads + 2 * n_kv) * AT_D + (size_t)kvh * R * AT_D;
-    for (int i = threadIdx.x; i < R * AT_D; i += 128) qs[i / AT_D][i % AT_D] = __half2float(qrow[i]) * scale;
-    __syncthreads();
+    const __half* tok = qkv + (size_t)t * (n_heads + 2 * n_kv) * AT_D;
+    const __half* qrow = tok + (size_t)kvh * R * AT_D;
     const int per = (ctx + nsplit - 1) / nsplit;
     const int p0 = split * per, p1 = min(ctx, p0 + per);
-    const __half* kb = kcache + ((size_t)seq * n_kv + kvh) * max_ctx * AT_D;
-    const __half* vb = vcache + ((size_t)seq * n_kv + kvh) * max_ctx * AT_D;
+    __half* kb = kcache + ((size_t)seq * n_kv + kvh) * max_ctx * AT_D;
+    __half* vb = vcache + ((size_t)seq * n_kv + kvh) * max_ctx * AT_D;
+    const bool rope = inv_freq != nullptr;
+    // position of the row that comes from shared memory instead of the cache (-1: none)
+    const int own = (rope && pos < max_ctx && pos >= p0 && pos < p1) ? pos : -1;
+    if (rope) {
+        if (threadIdx.x < AT_D / 2) {
+            const float ang = (float)pos * inv_freq[threadIdx.x];
+            cs_s[0][threadIdx.x] = __float2half_rn(cosf(ang) * attn_scaling);
+            cs_s[1][threadIdx.x] = __float2half_rn(sinf(ang) * attn_scaling);
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < R * AT_D; i += 128) {
+            const int r = i / AT_D, dd = i % AT_D, i2 = dd % (AT_D / 2);
+            const __half c = cs_s[0][i2], sn = cs_s[1][i2];
+            const __half x = qrow[i];
+            const __half y = (dd < AT_D / 2) ? __hneg(qrow[r * AT_D + dd + AT_D / 2]) : qrow[r * AT_D + dd - AT_D / 2];
+            qs[r][dd] = __half2float(__hadd(__hmul(x, c), __hmul(y, sn))) * scale;
+        }
+        if (own >= 0) {                            // this CTA holds the new token's position
+            const __half* krow = tok + (size_t)(n_heads + kvh) * AT_D;
+            const __half* vrow = tok + (size_t)(n_heads + n_kv + kvh) * AT_D;
+            const int dd = threadIdx.x, i2 = dd % (AT_D / 2);
+            const __half c = cs_s[0][i2], sn = cs_s[1][i2];
+            const __half y = (dd < AT_D / 2) ? __hneg(krow[dd + AT_D / 2]) : krow[dd - AT_D / 2];
+            const __half kr1 = __hadd(__hmul(krow[dd], c), __hmul(y, sn));
+            knew[dd] = kr1, vnew[dd] = vrow[dd];
+            kb[(size_t)pos * AT_D + dd] = kr1;
+            vb[(size_t)pos * AT_D + dd] = vrow[dd];
+        }
+    } else {
+        for (int i = threadIdx.x; i < R * AT_D; i += 128) qs[i / AT_D][i % AT_D] = __half2float(qrow[i]) * scale;
+    }
+    __syncthreads();
 
     float m[R], l[R], acc[R][4];
 #pragma unroll
@@ -170,9 +208,10 @@ __global__ void __launch_bounds__(128) attention_kernel(const __half* __restrict
         for (int r = 0; r < R; ++r) sc[r] = 0.0f;
         if (p < p1) {
             const uint4* kr = reinterpret_cast<const uint4*>(kb + (size_t)p * AT_D);
-#pragma unroll 4
+            const uint4* ks = reinterpret_cast<const uint4*>(knew);
+#pragma unroll
             for (int c = 0; c < AT_D / 8; ++c) {
-                const uint4 kv = __ldg(kr + c);
+                const uint4 kv = (p == own) ? ks[c] : __ldg(kr + c);
                 const __half2* kh = reinterpret_cast<const __half2*>(&kv);
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
@@ -205,7 +244,9 @@ __global__ void __launch_bounds__(128) attention_kernel(const __half* __restrict
             uint2 vv[8];
 #pragma unroll
             for (int u = 0; u < 8; ++u)
-                vv[u] = __ldg(reinterpret_cast<const uint2*>(vb + (size_t)min(base + j0 + u, max_ctx - 1) * AT_D) + lane);
+                vv[u] = (base + j0 + u == own)
+                            ? reinterpret_cast<const uint2*>(vnew)[lane]
+                            : __ldg(reinterpret_cast<const uint2*>(vb + (size_t)min(base + j0 + u, max_ctx - 1) * AT_D) + lane);
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
                 const __half2* vh = reinterpret_cast<const __half2*>(&vv[u]);
@@ -247,24 +288,36 @@ __global__ void __launch_bounds__(128) attention_kernel(const __half* __restrict
             if (dd == 0) pp[0] = gm, pp[1] = gl;
         }
     }
-}
-
-// merges the splits of one (token, head)                                   grid tokens * n_heads, 128 threads
-__global__ void __launch_bounds__(128) attention_combine_kernel(const float* __restrict__ part, __half* __restrict__ out,
-                                                                int nsplit) {
-    pdl_launch_dependents();
-    pdl_wait();
-    const float* pp = part + (size_t)blockIdx.x * nsplit * (AT_D + 2);
-    float gm = -INFINITY;
-    for (int s = 0; s < nsplit; ++s) gm = fmaxf(gm, pp[(size_t)s * (AT_D + 2)]);
-    float gl = 0.0f, ga = 0.0f;
-    for (int s = 0; s < nsplit; ++s) {
-        const float* q = pp + (size_t)s * (AT_D + 2);
-        const float c = (q[0] == -INFINITY) ? 0.0f : __expf(q[0] - gm);
-        gl += q[1] * c;
-        ga += q[2 + threadIdx.x] * c;
+    if (nsplit == 1) return;
+    // The split that arrives last merges all splits of its (token, KV head): no second launch.  Merging goes in split
+    // order whoever does it, so the result does not depend on the arrival order.
+    __shared__ int last_s;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned int old = atomicAdd(counters + blockIdx.x, 1u);
+        last_s = (old == (unsigned int)(nsplit - 1));
+        if (last_s) counters[blockIdx.x] = 0u;     // ready for the next launch
     }
-    out[(size_t)blockIdx.x * AT_D + threadIdx.x] = __float2half_rn(gl > 0.0f ? ga / gl : 0.0f);
+    __syncthreads();
+    if (!last_s) return;
+    __threadfence();
+    for (int i = threadIdx.x; i < R * AT_D; i += 128) {
+        const int r = i / AT_D, dd = i % AT_D;
+        const int head = kvh * R + r;
+        const float* pp = part + ((size_t)t * n_heads + head) * nsplit * (AT_D + 2);
+        float gm = -INFINITY;
+        for (int sp = 0; sp < nsplit; ++sp) gm = fmaxf(gm, __ldcg(pp + (size_t)sp * (AT_D + 2)));
+        float gl = 0.0f, ga = 0.0f;
+        for (int sp = 0; sp < nsplit; ++sp) {
+            const float* q = pp + (size_t)sp * (AT_D + 2);
+            const float m0 = __ldcg(q);
+            const float c = (m0 == -INFINITY) ? 0.0f : __expf(m0 - gm);
+            gl += __ldcg(q + 1) * c;
+            ga += __ldcg(q + 2 + dd) * c;
+        }
+        out[((size_t)t * n_heads + head) * AT_D + dd] = __float2half_rn(gl > 0.0f ? ga / gl : 0.0f);
+    }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -404,9 +457,9 @@ int sbvr_rope_append_f16(void* qkv, const int* positions, const float* inv_freq,
     return SBVR_OK;
 }
 
-int sbvr_attention_f16(const void* qkv, const void* kcache, const void* vcache, const int* positions, void* out,
-                       float* scratch, int tokens, int tokens_per_seq, int n_heads, int n_kv, int head_dim, int max_ctx,
-                       float scale, int nsplit, sbvr_stream_t stream) {
+static int attention_launch(const void* qkv, void* kcache, void* vcache, const int* positions, void* out, float* scratch,
+                            int tokens, int tokens_per_seq, int n_heads, int n_kv, int head_dim, int max_ctx, float scale,
+                            int nsplit, const float* inv_freq, float attn_scaling, sbvr_stream_t stream) {
     if (!qkv || !kcache || !vcache || !positions || !out) return SBVR_ERR_BAD_ARG;
     if (tokens < 1 || tokens_per_seq < 1 || tokens % tokens_per_seq || n_kv < 1 || n_heads % n_kv || max_ctx < 1 ||
         nsplit < 1 || nsplit > 64)
@@ -418,12 +471,14 @@ int sbvr_attention_f16(const void* qkv, const void* kcache, const void* vcache, 
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     const dim3 grid((unsigned)(tokens * n_kv), (unsigned)nsplit);
     const __half* q = reinterpret_cast<const __half*>(qkv);
-    const __half* kc = reinterpret_cast<const __half*>(kcache);
-    const __half* vc = reinterpret_cast<const __half*>(vcache);
+    __half* kc = reinterpret_cast<__half*>(kcache);
+    __half* vc = reinterpret_cast<__half*>(vcache);
     __half* o = reinterpret_cast<__half*>(out);
+    // the arrival counters of the splits sit behind the partial results
+    unsigned int* counters = reinterpret_cast<unsigned int*>(scratch + (size_t)tokens * n_heads * nsplit * (AT_D + 2));
 #define SBVR_ATT(RR)                                                                                              \
     SBVR_CUDA_TRY(launch_pdl(attention_kernel<RR>, grid, dim3(128), 0, st, q, kc, vc, positions, o, scratch,     \
-                             tokens_per_seq, n_heads, n_kv, max_ctx, scale, nsplit))
+                             counters, tokens_per_seq, n_heads, n_kv, max_ctx, scale, nsplit, inv_freq, attn_scaling))
     switch (R) {
         case 1: SBVR_ATT(1); break;
         case 2: SBVR_ATT(2); break;
@@ -432,10 +487,23 @@ int sbvr_attention_f16(const void* qkv, const void* kcache, const void* vcache, 
         default: return SBVR_ERR_UNSUPPORTED;
     }
 #undef SBVR_ATT
-    if (nsplit > 1)
-        SBVR_CUDA_TRY(launch_pdl(attention_combine_kernel, dim3(tokens * n_heads), dim3(128), 0, st,
-                                 static_cast<const float*>(scratch), o, nsplit));
+
     return SBVR_OK;
+}
+
+int sbvr_attention_f16(const void* qkv, const void* kcache, const void* vcache, const int* positions, void* out,
+                       float* scratch, int tokens, int tokens_per_seq, int n_heads, int n_kv, int head_dim, int max_ctx,
+                       float scale, int nsplit, sbvr_stream_t stream) {
+    return attention_launch(qkv, const_cast<void*>(kcache), const_cast<void*>(vcache), positions, out, scratch, tokens,
+                            tokens_per_seq, n_heads, n_kv, head_dim, max_ctx, scale, nsplit, nullptr, 1.0f, stream);
+}
+
+int sbvr_rope_attention_f16(const void* qkv, const int* positions, const float* inv_freq, float attn_scaling, void* kcache,
+                            void* vcache, void* out, float* scratch, int tokens, int n_heads, int n_kv, int head_dim,
+                            int max_ctx, float scale, int nsplit, sbvr_stream_t stream) {
+    if (!inv_freq) return SBVR_ERR_BAD_ARG;
+    return attention_launch(qkv, kcache, vcache, positions, out, scratch, tokens, 1, n_heads, n_kv, head_dim, max_ctx, scale,
+                            nsplit, inv_freq, attn_scaling, stream);
 }
 
 int sbvr_silu_mul_f16(const void* gate_up, void* out, int rows, int inter, sbvr_stream_t stream) {

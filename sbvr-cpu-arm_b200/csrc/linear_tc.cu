@@ -71,6 +71,13 @@ struct TcParams {
     __half* y;
     unsigned int* status;
     int N, K, KB, NT, C, cache_in_smem;
+    // what the activations are made of while they are brought in (XOp): nothing, SiLU(gate) * up, or
+    // RMSNorm(h + delta) * weight with the new residual written once
+    int x_op;
+    const __half* delta;
+    const __half* norm_w;
+    __half* h_out;
+    float eps;
 };
 
 __host__ __device__ constexpr int tc_sp(int S) { return S == 2 ? 2 : 4; }            // MMA rows per output row
@@ -416,7 +423,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) linear_tc_kernel(const TcParams
         load_tile();
         load_tile();
         pdl_wait();
-        {
+        if (p.x_op == SBVR_XOP_NONE) {
             const int nchunk = M * KB * 32;        // 16-byte pieces
             for (int c = ctid; c < nchunk; c += TC_CTHREADS) {
                 const int part = c & 31, blk = c >> 5;     // blk = m * KB + kb
@@ -426,8 +433,97 @@ __global__ void __launch_bounds__(TC_THREADS, 1) linear_tc_kernel(const TcParams
                              "l"(p.x + (size_t)m * p.K + (size_t)kb * 256 + part * 8)
                              : "memory");
             }
-            asm volatile("cp.async.commit_group;" ::: "memory");
+        } else if (p.x_op == SBVR_XOP_SILU_MUL) {
+            // x[m][k] = fp16(silu(g[m][k])) * u[m][k] with rows [g (K) | u (K)]: the activation of the MLP, formed here
+            // instead of in a kernel of its own (every CTA needs all of x anyway)
+            const int nchunk = M * KB * 32;
+            for (int c = ctid; c < nchunk; c += TC_CTHREADS) {
+                const int part = c & 31, blk = c >> 5;
+                const int m = blk / KB, kb = blk - m * KB;
+                const __half* gp = p.x + (size_t)m * 2 * p.K + (size_t)kb * 256 + part * 8;
+                const uint4 g = __ldg(reinterpret_cast<const uint4*>(gp));
+                const uint4 u = __ldg(reinterpret_cast<const uint4*>(gp + p.K));
+                const __half2* gh = reinterpret_cast<const __half2*>(&g);
+                const __half2* uh = reinterpret_cast<const __half2*>(&u);
+                uint4 o;
+                __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 f = __half22float2(gh[e]);
+                    oh[e] = __hmul2(__floats2half2_rn(f.x / (1.0f + expf(-f.x)), f.y / (1.0f + expf(-f.y))), uh[e]);
+                }
+                *reinterpret_cast<uint4*>(Bs + ((size_t)kb * M + m) * 1024 + part * 16) = o;
+            }
+        } else {
+            // x[m] = weight * fp16((h[m] + delta[m]) * rsqrt(mean((h[m] + delta[m])^2) + eps)): the residual add and the
+            // RMSNorm in front of the linear.  Pass 1 leaves h + delta in the staging area and sums the squares, pass 2
+            // scales in place; CTA 0 also writes the new residual (to a buffer other than h: other CTAs still read h).
+            float ss[M];
+#pragma unroll
+            for (int m = 0; m < M; ++m) ss[m] = 0.0f;
+            const int nchunk = M * KB * 32;
+            for (int c = ctid; c < nchunk; c += TC_CTHREADS) {
+                const int part = c & 31, blk = c >> 5;
+                const int m = blk / KB, kb = blk - m * KB;
+                const size_t off = (size_t)m * p.K + (size_t)kb * 256 + part * 8;
+                uint4 a = __ldg(reinterpret_cast<const uint4*>(p.x + off));
+                __half2* ah = reinterpret_cast<__half2*>(&a);
+                if (p.delta) {
+                    const uint4 b = __ldg(reinterpret_cast<const uint4*>(p.delta + off));
+                    const __half2* bh = reinterpret_cast<const __half2*>(&b);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) ah[e] = __hadd2(ah[e], bh[e]);
+                }
+                float sq = 0.0f;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 f = __half22float2(ah[e]);
+                    sq += f.x * f.x + f.y * f.y;
+                }
+#pragma unroll
+                for (int mm = 0; mm < M; ++mm) ss[mm] += (mm == m) ? sq : 0.0f;
+                *reinterpret_cast<uint4*>(Bs + ((size_t)kb * M + m) * 1024 + part * 16) = a;
+                if (p.h_out && blockIdx.x == 0) *reinterpret_cast<uint4*>(p.h_out + off) = a;
+            }
+            float* ssum = red;                     // [16 warps][M]: the hand-over area is not in use yet
+#pragma unroll
+            for (int m = 0; m < M; ++m) {
+                float v = ss[m];
+#pragma unroll
+                for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                if (lane == 0) ssum[warp * M + m] = v;
+            }
+            named_bar_sync(2, TC_CTHREADS);
+            float rs[M];
+#pragma unroll
+            for (int m = 0; m < M; ++m) {
+                float tot = 0.0f;
+                for (int w = 0; w < TC_WGS * 4; ++w) tot += ssum[w * M + m];
+                rs[m] = rsqrtf(tot / (float)p.K + p.eps);
+            }
+            for (int c = ctid; c < nchunk; c += TC_CTHREADS) {       // the same pieces this thread wrote above
+                const int part = c & 31, blk = c >> 5;
+                const int m = blk / KB, kb = blk - m * KB;
+                uint4* sp = reinterpret_cast<uint4*>(Bs + ((size_t)kb * M + m) * 1024 + part * 16);
+                const uint4 a = *sp;
+                const uint4 wv = __ldg(reinterpret_cast<const uint4*>(p.norm_w + (size_t)kb * 256 + part * 8));
+                const __half2* ah = reinterpret_cast<const __half2*>(&a);
+                const __half2* wh = reinterpret_cast<const __half2*>(&wv);
+                float r1 = 0.0f;
+#pragma unroll
+                for (int mm = 0; mm < M; ++mm) r1 = (mm == m) ? rs[mm] : r1;
+                uint4 o;
+                __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 f = __half22float2(ah[e]);
+                    oh[e] = __hmul2(wh[e], __floats2half2_rn(f.x * r1, f.y * r1));
+                }
+                *sp = o;
+            }
+            named_bar_sync(2, TC_CTHREADS);        // `red` is free again before anybody hands sums over
         }
+        asm volatile("cp.async.commit_group;" ::: "memory");
         TC_PROF_MARK(10);
         TC_PROF_MARK(5);
         asm volatile("cp.async.wait_group 0;" ::: "memory");       // this thread's pieces of x have landed
@@ -808,7 +904,7 @@ static int tc_launch_g(const TcParams& p, int G, int M, int idxb, int grid, int 
 }
 
 int launch_linear_tc(const __half* x, const PackedW& w, const __half* bias, __half* y, int M, sbvr_workspace* ws,
-                     cudaStream_t st) {
+                     cudaStream_t st, const XOp* xop) {
     if (!linear_tc_supported(w, M)) return SBVR_ERR_UNSUPPORTED;
     if (!ws) return SBVR_ERR_WORKSPACE;
     if (reinterpret_cast<uintptr_t>(x) & 15) return SBVR_ERR_ALIGN;      // x is fetched with 16-byte cp.async
@@ -822,6 +918,15 @@ int launch_linear_tc(const __half* x, const PackedW& w, const __half* bias, __ha
     TcParams p;
     p.x = x, p.bvr = w.bvr, p.idx = w.idx, p.coeff = w.coeff, p.bias = bias, p.y = y;
     p.status = ws->status;
+    p.x_op = xop ? xop->op : SBVR_XOP_NONE;
+    p.delta = xop ? xop->delta : nullptr, p.norm_w = xop ? xop->norm_w : nullptr, p.h_out = xop ? xop->h_out : nullptr;
+    p.eps = xop ? xop->eps : 0.0f;
+    if (p.x_op == SBVR_XOP_ADD_RMSNORM) {
+        if (!p.norm_w || p.h_out == x) return SBVR_ERR_BAD_ARG;
+        if ((reinterpret_cast<uintptr_t>(p.delta) | reinterpret_cast<uintptr_t>(p.norm_w) |
+             reinterpret_cast<uintptr_t>(p.h_out)) & 15)
+            return SBVR_ERR_ALIGN;
+    }
     p.N = w.N, p.K = w.K, p.KB = pl.KB, p.NT = pl.NT, p.C = w.C, p.cache_in_smem = pl.cache_in_smem;
     switch (w.S) {
         case 2: return tc_launch_g<2>(p, w.G, M, w.idx_bytes, pl.grid, pl.smem, st);

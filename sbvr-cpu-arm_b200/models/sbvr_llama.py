@@ -24,6 +24,7 @@ import torch
 
 import sbvr as _sbvr
 from sbvr import _lib
+from sbvr.core import XOP_ADD_RMSNORM, XOP_SILU_MUL, linear_fused
 from sbvr.core import linear as sbvr_linear
 from sbvr.core import sbvr as sbvr_tensor
 
@@ -134,6 +135,7 @@ class _Buffers:
     ids: torch.Tensor
     positions: torch.Tensor
     h: torch.Tensor
+    h2: torch.Tensor
     xn: torch.Tensor
     qkv: torch.Tensor
     ao: torch.Tensor
@@ -182,6 +184,7 @@ class SBVRLlamaForCausalLM(torch.nn.Module):
         self._graph = None
         self._stream = None
         self._comm = None
+        self.fuse_glue = True                      # fold norm / SiLU into the decode linears where the kernel allows
         self._argmax_scratch = torch.empty(256, dtype=torch.float32, device=self.device)
 
     # ------------------------------------------------------------------ weights
@@ -263,15 +266,15 @@ class SBVRLlamaForCausalLM(torch.nn.Module):
             tokens=tokens,
             ids=torch.zeros(tokens, dtype=torch.int32, device=dev),
             positions=torch.zeros(tokens, dtype=torch.int32, device=dev),
-            h=torch.empty((tokens, H), **f16), xn=torch.empty((tokens, H), **f16),
+            h=torch.empty((tokens, H), **f16), h2=torch.empty((tokens, H), **f16), xn=torch.empty((tokens, H), **f16),
             qkv=torch.empty((tokens, (self.n_heads + 2 * self.n_kv) * c.head_dim), **f16),
             ao=torch.empty((tokens, self.n_heads * c.head_dim), **f16), o=torch.empty((tokens, H), **f16),
             gu=torch.empty((tokens, 2 * self.inter), **f16), act=torch.empty((tokens, self.inter), **f16),
             down=torch.empty((tokens, H), **f16),
             logits=torch.empty((rows_out, self.vocab_local), **f16),
             next_ids=torch.zeros(rows_out, dtype=torch.int32, device=dev),
-            att_scratch=(torch.empty(tokens * self.n_heads * nsplit * 130, dtype=torch.float32, device=dev)
-                         if nsplit > 1 else None))
+            att_scratch=(torch.zeros(tokens * self.n_heads * nsplit * 130 + tokens * self.n_kv, dtype=torch.float32,
+                                     device=dev) if nsplit > 1 else None))
         if self.tp_size > 1:
             b.extra["gathered"] = torch.empty((self.tp_size, rows_out, self.vocab_local), **f16)
         self._bufs[key] = b
@@ -297,56 +300,82 @@ class SBVRLlamaForCausalLM(torch.nn.Module):
         scale = 1.0 / math.sqrt(c.head_dim)
         nsplit = self._nsplit(T)
         ck = _lib.check
-        ck(L.sbvr_embedding_f16(b.ids.data_ptr(), self.embed_tokens.data_ptr(), b.h.data_ptr(), T, H, st), "embedding")
         # Tensor parallel with few rows: the partial outputs of o and down go to symmetric memory and one fused
         # kernel all-reduces them, adds the residual and applies the next RMSNorm.  Otherwise NCCL + add_rmsnorm.
         comm = self._comm if (self._comm is not None and T <= self._comm.max_rows) else None
         ws = _lib.workspace(self.device.index or 0, st) if comm is not None else None
         n_layers = len(self.layers)
+        # Up to four rows (decode): the residual add + RMSNorm in front of q|k|v, gate|up and lm_head and the
+        # SiLU * up in front of down are folded into those linears' kernels.  The folded norm cannot update the
+        # residual in place (other CTAs still read it), so the residual alternates between two buffers.
+        fuse = self.fuse_glue and T <= 4
+        hc, ho = b.h, b.h2                         # current residual, spare buffer
+
+        def norm_linear(lin, delta, weight, out, keep_residual=True):
+            """out = lin(rmsnorm(hc + delta) * weight); the residual becomes hc + delta."""
+            nonlocal hc, ho
+            if fuse and isinstance(lin, SBVRLinear) and linear_fused(
+                    XOP_ADD_RMSNORM, hc, lin.weight, out, delta=delta, norm_weight=weight,
+                    h_out=ho if keep_residual else None, eps=eps, bias=lin.bias):
+                if keep_residual:
+                    hc, ho = ho, hc
+                return
+            ck(L.sbvr_add_rmsnorm_f16(hc.data_ptr(), None if delta is None else delta.data_ptr(), weight.data_ptr(),
+                                      hc.data_ptr() if keep_residual else None, b.xn.data_ptr(), T, H, eps, st), "rmsnorm")
+            lin(b.xn, out=out)
+
+        ck(L.sbvr_embedding_f16(b.ids.data_ptr(), self.embed_tokens.data_ptr(), hc.data_ptr(), T, H, st), "embedding")
         delta, normed = None, False
         for li, layer in enumerate(self.layers):
-            if not normed:
-                ck(L.sbvr_add_rmsnorm_f16(b.h.data_ptr(), None if delta is None else delta.data_ptr(),
-                                          layer.input_layernorm_weight.data_ptr(), b.h.data_ptr(), b.xn.data_ptr(), T, H,
-                                          eps, st), "rmsnorm")
-            layer.qkv_proj(b.xn, out=b.qkv)
-            ck(L.sbvr_rope_append_f16(b.qkv.data_ptr(), b.positions.data_ptr(), self.inv_freq.data_ptr(),
-                                      float(self.attention_scaling), self.kcache[li].data_ptr(),
-                                      self.vcache[li].data_ptr(), T, tokens_per_seq, self.n_heads, self.n_kv,
-                                      c.head_dim, self.max_ctx, st), "rope")
-            ck(L.sbvr_attention_f16(b.qkv.data_ptr(), self.kcache[li].data_ptr(), self.vcache[li].data_ptr(),
-                                    b.positions.data_ptr(), b.ao.data_ptr(),
-                                    None if b.att_scratch is None else b.att_scratch.data_ptr(), T, tokens_per_seq,
-                                    self.n_heads, self.n_kv, c.head_dim, self.max_ctx, scale, nsplit, st), "attention")
+            if normed:
+                layer.qkv_proj(b.xn, out=b.qkv)
+            else:
+                norm_linear(layer.qkv_proj, delta, layer.input_layernorm_weight, b.qkv)
+            att_scratch = None if b.att_scratch is None else b.att_scratch.data_ptr()
+            if tokens_per_seq == 1 and self.fuse_glue:     # decode: rotary embedding and cache append inside attention
+                ck(L.sbvr_rope_attention_f16(b.qkv.data_ptr(), b.positions.data_ptr(), self.inv_freq.data_ptr(),
+                                             float(self.attention_scaling), self.kcache[li].data_ptr(),
+                                             self.vcache[li].data_ptr(), b.ao.data_ptr(), att_scratch, T, self.n_heads,
+                                             self.n_kv, c.head_dim, self.max_ctx, scale, nsplit, st), "rope_attention")
+            else:
+                ck(L.sbvr_rope_append_f16(b.qkv.data_ptr(), b.positions.data_ptr(), self.inv_freq.data_ptr(),
+                                          float(self.attention_scaling), self.kcache[li].data_ptr(),
+                                          self.vcache[li].data_ptr(), T, tokens_per_seq, self.n_heads, self.n_kv,
+                                          c.head_dim, self.max_ctx, st), "rope")
+                ck(L.sbvr_attention_f16(b.qkv.data_ptr(), self.kcache[li].data_ptr(), self.vcache[li].data_ptr(),
+                                        b.positions.data_ptr(), b.ao.data_ptr(), att_scratch, T, tokens_per_seq,
+                                        self.n_heads, self.n_kv, c.head_dim, self.max_ctx, scale, nsplit, st), "attention")
             if comm is not None:
                 layer.o_proj(b.ao, out=comm.partial_out(2 * li, T))
-                comm.reduce_add_rmsnorm(2 * li, b.h, layer.post_attention_layernorm_weight, b.xn, T, eps, ws, st)
+                comm.reduce_add_rmsnorm(2 * li, hc, layer.post_attention_layernorm_weight, b.xn, T, eps, ws, st)
+                layer.gate_up_proj(b.xn, out=b.gu)
             else:
                 layer.o_proj(b.ao, out=b.o)
                 self._all_reduce(b.o)
-                ck(L.sbvr_add_rmsnorm_f16(b.h.data_ptr(), b.o.data_ptr(), layer.post_attention_layernorm_weight.data_ptr(),
-                                          b.h.data_ptr(), b.xn.data_ptr(), T, H, eps, st), "rmsnorm")
-            layer.gate_up_proj(b.xn, out=b.gu)
-            ck(L.sbvr_silu_mul_f16(b.gu.data_ptr(), b.act.data_ptr(), T, self.inter, st), "silu_mul")
+                norm_linear(layer.gate_up_proj, b.o, layer.post_attention_layernorm_weight, b.gu)
+            down_out = comm.partial_out(2 * li + 1, T) if comm is not None else b.down
+            if not (fuse and isinstance(layer.down_proj, SBVRLinear) and
+                    linear_fused(XOP_SILU_MUL, b.gu, layer.down_proj.weight, down_out, bias=layer.down_proj.bias)):
+                ck(L.sbvr_silu_mul_f16(b.gu.data_ptr(), b.act.data_ptr(), T, self.inter, st), "silu_mul")
+                layer.down_proj(b.act, out=down_out)
             if comm is not None:
-                layer.down_proj(b.act, out=comm.partial_out(2 * li + 1, T))
                 nw = self.layers[li + 1].input_layernorm_weight if li + 1 < n_layers else self.norm_weight
-                comm.reduce_add_rmsnorm(2 * li + 1, b.h, nw, b.xn, T, eps, ws, st)
+                comm.reduce_add_rmsnorm(2 * li + 1, hc, nw, b.xn, T, eps, ws, st)
                 delta, normed = None, True
             else:
-                layer.down_proj(b.act, out=b.down)
                 self._all_reduce(b.down)
                 delta, normed = b.down, False
-        if not normed:
-            ck(L.sbvr_add_rmsnorm_f16(b.h.data_ptr(), None if delta is None else delta.data_ptr(),
-                                      self.norm_weight.data_ptr(), None, b.xn.data_ptr(), T, H, eps, st), "rmsnorm")
+        rows_sel = last_only and tokens_per_seq > 1
+        if normed or rows_sel:
+            if not normed:
+                ck(L.sbvr_add_rmsnorm_f16(hc.data_ptr(), None if delta is None else delta.data_ptr(),
+                                          self.norm_weight.data_ptr(), None, b.xn.data_ptr(), T, H, eps, st), "rmsnorm")
+            rows = b.xn.view(-1, tokens_per_seq, H)[:, -1, :].contiguous() if rows_sel else b.xn
+            self.lm_head(rows, out=b.logits)
+        else:
+            norm_linear(self.lm_head, delta, self.norm_weight, b.logits, keep_residual=False)
         if self._comm is not None:
             self._comm.end_step()
-        if last_only and tokens_per_seq > 1:
-            rows = b.xn.view(-1, tokens_per_seq, H)[:, -1, :].contiguous()
-        else:
-            rows = b.xn
-        self.lm_head(rows, out=b.logits)
         if self.tp_size > 1:
             g = b.extra["gathered"]
             torch.distributed.all_gather_into_tensor(g, b.logits, group=self.tp_group)

@@ -307,6 +307,35 @@ def linear(x: torch.Tensor, w: sbvr, bias: Optional[torch.Tensor] = None, algo: 
     return y.view(*lead, N)
 
 
+XOP_SILU_MUL, XOP_ADD_RMSNORM = 1, 2
+
+
+@torch.inference_mode()
+def linear_fused(op: int, x: torch.Tensor, w: sbvr, out: torch.Tensor, delta: Optional[torch.Tensor] = None,
+                 norm_weight: Optional[torch.Tensor] = None, h_out: Optional[torch.Tensor] = None, eps: float = 0.0,
+                 bias: Optional[torch.Tensor] = None) -> bool:
+    """Decode linear with the op in front of it folded into the kernel (`sbvr_linear_fused_f16`):
+    XOP_SILU_MUL: out = (silu(x[:, :K]) * x[:, K:]) @ W.T;  XOP_ADD_RMSNORM: out = rmsnorm(x + delta) * norm_weight @ W.T
+    with x + delta stored to h_out.  Returns False (and computes nothing) where the decode kernel does not apply."""
+    dev = w.bvr.device
+    di = _cuda_index(dev)
+    Kp, N = w.in_features_padded, w.out_features
+    M = x.shape[0]
+    if M > 4 or int(w.original_data_shape[-1]) != Kp or not x.is_contiguous():
+        return False
+    b, ix, ib, c, C = w._abi_args()
+    with torch.cuda.device(di):
+        st = torch.cuda.current_stream().cuda_stream
+        ws = _lib.workspace(di, st)
+        rc = _lib.lib.sbvr_linear_fused_f16(op, x.data_ptr(), _ptr(delta), _ptr(norm_weight), _ptr(h_out), float(eps), b,
+                                            ix, ib, c, C, _ptr(bias), out.data_ptr(), M, N, Kp, w.num_sums, w.bvr_len,
+                                            ws.handle, st)
+    if rc == -7:
+        return False
+    _lib.check(rc, "sbvr_linear_fused_f16")
+    return True
+
+
 def mm_T(lhs, rhs: sbvr, bias=None):
     """`lhs @ rhs.T + bias` (reference `mm_T`, sbvr/core.py:1029-1039).  `lhs` may be an fp16 tensor or, as in
     the reference, an `sbvr` object, which is decoded on the GPU first."""

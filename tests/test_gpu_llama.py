@@ -154,7 +154,7 @@ def test_attention_kernel_against_softmax(ctx, nsplit):
     V = torch.randn((B, nkv, 1300, d), device="cuda", generator=g).half()
     pos = torch.full((B,), ctx - 1, dtype=torch.int32, device="cuda")
     out = torch.empty((B, nh * d), dtype=torch.float16, device="cuda")
-    scratch = torch.empty(B * nh * nsplit * 130, dtype=torch.float32, device="cuda")
+    scratch = torch.zeros(B * nh * nsplit * 130 + B * nkv, dtype=torch.float32, device="cuda")
     _lib.check(_lib.lib.sbvr_attention_f16(qkv.data_ptr(), K.data_ptr(), V.data_ptr(), pos.data_ptr(), out.data_ptr(),
                                            scratch.data_ptr(), B, 1, nh, nkv, d, 1300, d ** -0.5, nsplit,
                                            torch.cuda.current_stream().cuda_stream))
@@ -206,3 +206,36 @@ def test_model_from_reference_style_directory(tmp_path):
     err = ((logits - ref).abs().max() / ref.abs().max()).item()
     assert err <= TOL, err
     assert torch.equal(m.generate(ids, 5, use_graph=True), m.generate(ids, 5, use_graph=False))
+
+
+@pytest.mark.parametrize("ctx,nsplit", [(1, 1), (40, 1), (300, 4), (1280, 16)])
+def test_rope_attention_equals_rope_then_attention(ctx, nsplit):
+    """The decode kernel that rotates q / k and appends k, v itself gives the bits of the two separate kernels."""
+    from sbvr import _lib
+    nh, nkv, d, B, mc = 8, 2, 128, 3, 1300
+    g = torch.Generator(device="cuda").manual_seed(ctx + 1)
+    qkv = torch.randn((B, (nh + 2 * nkv) * d), device="cuda", generator=g).half()
+    K = torch.randn((B, nkv, mc, d), device="cuda", generator=g).half()
+    V = torch.randn((B, nkv, mc, d), device="cuda", generator=g).half()
+    pos = torch.full((B,), ctx - 1, dtype=torch.int32, device="cuda")
+    inv = (1.0 / (500000.0 ** (torch.arange(0, d, 2, dtype=torch.float32) / d))).cuda()
+    st = torch.cuda.current_stream().cuda_stream
+    n_scr = B * nh * nsplit * 130 + B * nkv
+    # separate kernels
+    q1, K1, V1 = qkv.clone(), K.clone(), V.clone()
+    o1 = torch.empty((B, nh * d), dtype=torch.float16, device="cuda")
+    s1 = torch.zeros(n_scr, dtype=torch.float32, device="cuda")
+    _lib.check(_lib.lib.sbvr_rope_append_f16(q1.data_ptr(), pos.data_ptr(), inv.data_ptr(), 1.0, K1.data_ptr(), V1.data_ptr(),
+                                             B, 1, nh, nkv, d, mc, st))
+    _lib.check(_lib.lib.sbvr_attention_f16(q1.data_ptr(), K1.data_ptr(), V1.data_ptr(), pos.data_ptr(), o1.data_ptr(),
+                                           s1.data_ptr(), B, 1, nh, nkv, d, mc, d ** -0.5, nsplit, st))
+    # fused, twice (the arrival counters must come back to zero)
+    K2, V2 = K.clone(), V.clone()
+    o2 = torch.empty_like(o1)
+    s2 = torch.zeros(n_scr, dtype=torch.float32, device="cuda")
+    for _ in range(2):
+        _lib.check(_lib.lib.sbvr_rope_attention_f16(qkv.data_ptr(), pos.data_ptr(), inv.data_ptr(), 1.0, K2.data_ptr(),
+                                                    V2.data_ptr(), o2.data_ptr(), s2.data_ptr(), B, nh, nkv, d, mc,
+                                                    d ** -0.5, nsplit, st))
+    assert torch.equal(K1, K2) and torch.equal(V1, V2)
+    assert torch.equal(o1, o2)

@@ -260,3 +260,54 @@ def test_linear_fewer_k_blocks_than_warpgroups(K, M):
     y = h2n(sbvr.linear(torch.from_numpy(x).cuda(), w, None, algo=2))
     assert O.max_rel_err(y, ref) <= TOL
     check_status()
+
+
+@pytest.mark.parametrize("M", [1, 2, 4])
+@pytest.mark.parametrize("K", [1024, 3584])
+def test_fused_silu_mul_linear_equals_separate_kernels(M, K):
+    """SiLU(gate) * up folded into the decode GEMV gives the bits of sbvr_silu_mul_f16 followed by sbvr_linear_f16."""
+    import sbvr
+    from sbvr import _lib
+    from sbvr.core import XOP_SILU_MUL, linear_fused
+    N, S = 512, 4
+    p = O.make_packed(N, K, S, G=256, mode="u16", C=1024, seed=K + M)
+    w = to_sbvr(p)
+    g = torch.Generator(device="cuda").manual_seed(M)
+    gu = torch.randn((M, 2 * K), device="cuda", generator=g).half()
+    act = torch.empty((M, K), dtype=torch.float16, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    _lib.check(_lib.lib.sbvr_silu_mul_f16(gu.data_ptr(), act.data_ptr(), M, K, st))
+    y_sep = sbvr.linear(act, w, None, algo=2)
+    y = torch.empty_like(y_sep)
+    assert linear_fused(XOP_SILU_MUL, gu, w, y)
+    assert torch.equal(y, y_sep)
+    ref = O.linear_c(h2n(act), p["bvr"], p["coeff_idx"], p["coeff"], G=256)
+    assert O.max_rel_err(h2n(y), ref) <= TOL
+    check_status()
+
+
+@pytest.mark.parametrize("M", [1, 3])
+@pytest.mark.parametrize("with_delta", [True, False])
+def test_fused_add_rmsnorm_linear(M, with_delta):
+    """Residual add + RMSNorm folded into the decode GEMV: the new residual is exact, the product matches the
+    separate kernels (only the fp32 summation order of the mean square differs)."""
+    import sbvr
+    from sbvr import _lib
+    from sbvr.core import XOP_ADD_RMSNORM, linear_fused
+    N, K, S = 768, 2048, 4
+    p = O.make_packed(N, K, S, G=256, mode="u8", seed=M + 7)
+    w = to_sbvr(p)
+    g = torch.Generator(device="cuda").manual_seed(3 * M)
+    h = torch.randn((M, K), device="cuda", generator=g).half()
+    d = torch.randn((M, K), device="cuda", generator=g).half() if with_delta else None
+    nw = (1 + 0.2 * torch.randn(K, device="cuda", generator=g)).half()
+    st = torch.cuda.current_stream().cuda_stream
+    h_sep, xn = torch.empty_like(h), torch.empty_like(h)
+    _lib.check(_lib.lib.sbvr_add_rmsnorm_f16(h.data_ptr(), None if d is None else d.data_ptr(), nw.data_ptr(),
+                                             h_sep.data_ptr(), xn.data_ptr(), M, K, 1e-5, st))
+    y_sep = sbvr.linear(xn, w, None, algo=2)
+    y, h_out = torch.empty_like(y_sep), torch.empty_like(h)
+    assert linear_fused(XOP_ADD_RMSNORM, h, w, y, delta=d, norm_weight=nw, h_out=h_out, eps=1e-5)
+    assert torch.equal(h_out, h_sep)
+    assert ((y.float() - y_sep.float()).abs().max() / y_sep.float().abs().max()).item() < 2e-3
+    check_status()
