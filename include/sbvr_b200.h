@@ -143,9 +143,8 @@ SBVR_API int sbvr_rope_append_f16(void* qkv, const int* positions, const float* 
 /* out[token][head][:] = softmax(q . K^T * scale) . V over cache positions 0 .. positions[token] of the token's
  * sequence, grouped-query (n_heads % n_kv == 0, ratio 1, 2, 4 or 8), head_dim 128.  Serves decode (one token per
  * sequence) and causal prefill (every token attends up to itself; its k, v must be in the cache already).
- * nsplit > 1 splits the positions over CTAs (decode at long context); the split that finishes last merges them.  It
- * needs `scratch` of tokens * n_heads * nsplit * 130 floats followed by tokens * n_kv 32-bit counters that are zero
- * before the first call (every call leaves them zero).  repeat_kv + eager_attention_forward (models/sbvr_llama.py:243-278). */
+ * nsplit > 1 splits the positions over CTAs (decode at long context), a second small launch merges the splits; it
+ * needs `scratch` of tokens * n_heads * nsplit * 130 floats.  repeat_kv + eager_attention_forward (models/sbvr_llama.py:243-278). */
 SBVR_API int sbvr_attention_f16(const void* qkv, const void* kcache, const void* vcache, const int* positions,
                                 void* out, float* scratch, int tokens, int tokens_per_seq, int n_heads, int n_kv,
                                 int head_dim, int max_ctx, float scale, int nsplit, sbvr_stream_t stream);

@@ -134,8 +134,7 @@ constexpr int AT_RMAX = 8;
 template <int R>
 __global__ void __launch_bounds__(128) attention_kernel(const __half* __restrict__ qkv, __half* kcache, __half* vcache,
                                                         const int* __restrict__ positions, __half* __restrict__ out,
-                                                        float* __restrict__ part, unsigned int* __restrict__ counters,
-                                                        int tokens_per_seq, int n_heads, int n_kv, int max_ctx, float scale,
+                                                        float* __restrict__ part, int tokens_per_seq, int n_heads, int n_kv, int max_ctx, float scale,
                                                         int nsplit, const float* __restrict__ inv_freq, float attn_scaling) {
     __shared__ float qs[R][AT_D];
     __shared__ float wm[4][R], wl[4][R];
@@ -288,35 +287,169 @@ __global__ void __launch_bounds__(128) attention_kernel(const __half* __restrict
             if (dd == 0) pp[0] = gm, pp[1] = gl;
         }
     }
-    if (nsplit == 1) return;
-    // The split that arrives last merges all splits of its (token, KV head): no second launch.  Merging goes in split
-    // order whoever does it, so the result does not depend on the arrival order.
-    __shared__ int last_s;
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        const unsigned int old = atomicAdd(counters + blockIdx.x, 1u);
-        last_s = (old == (unsigned int)(nsplit - 1));
-        if (last_s) counters[blockIdx.x] = 0u;     // ready for the next launch
+}
+
+// merges the splits of one (token, head)                                   grid tokens * n_heads, 128 threads
+__global__ void __launch_bounds__(128) attention_combine_kernel(const float* __restrict__ part, __half* __restrict__ out,
+                                                                int nsplit) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const float* pp = part + (size_t)blockIdx.x * nsplit * (AT_D + 2);
+    // all loads of a batch of eight splits are issued before any is used (one L2 latency per batch, not per split)
+    float gm = -INFINITY;
+    for (int s0 = 0; s0 < nsplit; s0 += 8) {
+        float mv[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) mv[u] = (s0 + u < nsplit) ? pp[(size_t)(s0 + u) * (AT_D + 2)] : -INFINITY;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) gm = fmaxf(gm, mv[u]);
+    }
+    float gl = 0.0f, ga = 0.0f;
+    for (int s0 = 0; s0 < nsplit; s0 += 8) {
+        float mv[8], lv[8], av[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const bool on = s0 + u < nsplit;
+            const float* q = pp + (size_t)(on ? s0 + u : 0) * (AT_D + 2);
+            mv[u] = on ? q[0] : -INFINITY;
+            lv[u] = on ? q[1] : 0.0f;
+            av[u] = on ? q[2 + threadIdx.x] : 0.0f;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const float c = (mv[u] == -INFINITY) ? 0.0f : __expf(mv[u] - gm);
+            gl += lv[u] * c;
+            ga += av[u] * c;
+        }
+    }
+    out[(size_t)blockIdx.x * AT_D + threadIdx.x] = __float2half_rn(gl > 0.0f ? ga / gl : 0.0f);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Causal prefill: QB consecutive tokens of a sequence share a CTA, so that a K or V row is fetched once for
+// 16 = QB * R (query token, query head) pairs instead of once per token.  grid sequences * n_kv * ceil(tps / QB).
+// Same arithmetic as attention_kernel: scores and probabilities in fp32, running maximum per pair.
+// ---------------------------------------------------------------------------------------------
+template <int R>
+__global__ void __launch_bounds__(128) attention_block_kernel(const __half* __restrict__ qkv, const __half* __restrict__ kcache,
+                                                              const __half* __restrict__ vcache,
+                                                              const int* __restrict__ positions, __half* __restrict__ out,
+                                                              int tokens_per_seq, int n_heads, int n_kv, int max_ctx,
+                                                              float scale) {
+    constexpr int QB = 16 / R, NQ = 16;
+    __shared__ float qs[NQ][AT_D];
+    __shared__ float wm[4][NQ], wl[4][NQ];
+    __shared__ float wacc[4][NQ][AT_D];
+    __shared__ int ctx_s[QB];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int nblk = (tokens_per_seq + QB - 1) / QB;
+    const int qblk = blockIdx.x % nblk, rest = blockIdx.x / nblk;
+    const int kvh = rest % n_kv, seq = rest / n_kv;
+    const int t0 = seq * tokens_per_seq + qblk * QB;
+    const int nq = min(QB, tokens_per_seq - qblk * QB);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x < QB) ctx_s[threadIdx.x] = (threadIdx.x < nq) ? min(positions[t0 + threadIdx.x] + 1, max_ctx) : 0;
+    for (int i = threadIdx.x; i < NQ * AT_D; i += 128) {
+        const int q = i / AT_D, dd = i % AT_D, j = q / R, r = q % R;
+        qs[q][dd] = (j < nq) ? __half2float(qkv[(size_t)(t0 + j) * (n_heads + 2 * n_kv) * AT_D +
+                                                 (size_t)(kvh * R + r) * AT_D + dd]) * scale
+                             : 0.0f;
     }
     __syncthreads();
-    if (!last_s) return;
-    __threadfence();
-    for (int i = threadIdx.x; i < R * AT_D; i += 128) {
-        const int r = i / AT_D, dd = i % AT_D;
-        const int head = kvh * R + r;
-        const float* pp = part + ((size_t)t * n_heads + head) * nsplit * (AT_D + 2);
-        float gm = -INFINITY;
-        for (int sp = 0; sp < nsplit; ++sp) gm = fmaxf(gm, __ldcg(pp + (size_t)sp * (AT_D + 2)));
-        float gl = 0.0f, ga = 0.0f;
-        for (int sp = 0; sp < nsplit; ++sp) {
-            const float* q = pp + (size_t)sp * (AT_D + 2);
-            const float m0 = __ldcg(q);
-            const float c = (m0 == -INFINITY) ? 0.0f : __expf(m0 - gm);
-            gl += __ldcg(q + 1) * c;
-            ga += __ldcg(q + 2 + dd) * c;
+    int P = 0;
+#pragma unroll
+    for (int j = 0; j < QB; ++j) P = max(P, ctx_s[j]);
+    const __half* kb = kcache + ((size_t)seq * n_kv + kvh) * max_ctx * AT_D;
+    const __half* vb = vcache + ((size_t)seq * n_kv + kvh) * max_ctx * AT_D;
+
+    float m[NQ], l[NQ], acc[NQ][4];
+#pragma unroll
+    for (int q = 0; q < NQ; ++q) {
+        m[q] = -INFINITY, l[q] = 0.0f;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[q][e] = 0.0f;
+    }
+    for (int base = warp * 32; base < P; base += 128) {
+        const int p = base + lane;
+        float sc[NQ];
+#pragma unroll
+        for (int q = 0; q < NQ; ++q) sc[q] = 0.0f;
+        if (p < P) {
+            const uint4* kr = reinterpret_cast<const uint4*>(kb + (size_t)p * AT_D);
+#pragma unroll 2
+            for (int c = 0; c < AT_D / 8; ++c) {
+                const uint4 kv = __ldg(kr + c);
+                const __half2* kh = reinterpret_cast<const __half2*>(&kv);
+                float kf[8];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 f = __half22float2(kh[e]);
+                    kf[2 * e] = f.x, kf[2 * e + 1] = f.y;
+                }
+#pragma unroll
+                for (int q = 0; q < NQ; ++q) {
+                    const float4 a = *reinterpret_cast<const float4*>(&qs[q][c * 8]);
+                    const float4 b = *reinterpret_cast<const float4*>(&qs[q][c * 8 + 4]);
+                    sc[q] += kf[0] * a.x + kf[1] * a.y + kf[2] * a.z + kf[3] * a.w + kf[4] * b.x + kf[5] * b.y +
+                             kf[6] * b.z + kf[7] * b.w;
+                }
+            }
         }
-        out[((size_t)t * n_heads + head) * AT_D + dd] = __float2half_rn(gl > 0.0f ? ga / gl : 0.0f);
+        float w[NQ];
+#pragma unroll
+        for (int q = 0; q < NQ; ++q) {
+            const bool on = p < ctx_s[q / R];      // causal: token j sees positions up to its own
+            float cm = on ? sc[q] : -INFINITY;
+#pragma unroll
+            for (int o = 16; o; o >>= 1) cm = fmaxf(cm, __shfl_xor_sync(0xffffffffu, cm, o));
+            const float nm = fmaxf(m[q], cm);
+            const float corr = (m[q] == -INFINITY) ? 0.0f : __expf(m[q] - nm);
+            w[q] = on ? __expf(sc[q] - nm) : 0.0f;
+            l[q] = l[q] * corr + warp_sum(w[q]);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[q][e] *= corr;
+            m[q] = nm;
+        }
+        const int np = min(32, P - base);
+        for (int j0 = 0; j0 < np; j0 += 4) {       // four V rows in flight; rows past the end carry weight 0
+            uint2 vv[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                vv[u] = __ldg(reinterpret_cast<const uint2*>(vb + (size_t)min(base + j0 + u, max_ctx - 1) * AT_D) + lane);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const __half2* vh = reinterpret_cast<const __half2*>(&vv[u]);
+                const float2 f0 = __half22float2(vh[0]), f1 = __half22float2(vh[1]);
+#pragma unroll
+                for (int q = 0; q < NQ; ++q) {
+                    const float wj = __shfl_sync(0xffffffffu, w[q], j0 + u);
+                    acc[q][0] += wj * f0.x, acc[q][1] += wj * f0.y, acc[q][2] += wj * f1.x, acc[q][3] += wj * f1.y;
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int q = 0; q < NQ; ++q) {
+        if (lane == 0) wm[warp][q] = m[q], wl[warp][q] = l[q];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) wacc[warp][q][lane * 4 + e] = acc[q][e];
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < NQ * AT_D; i += 128) {
+        const int q = i / AT_D, dd = i % AT_D, j = q / R, r = q % R;
+        if (j >= nq) continue;
+        float gm = -INFINITY;
+#pragma unroll
+        for (int w4 = 0; w4 < 4; ++w4) gm = fmaxf(gm, wm[w4][q]);
+        float gl = 0.0f, ga = 0.0f;
+#pragma unroll
+        for (int w4 = 0; w4 < 4; ++w4) {
+            const float c = (wm[w4][q] == -INFINITY) ? 0.0f : __expf(wm[w4][q] - gm);
+            gl += wl[w4][q] * c;
+            ga += wacc[w4][q][dd] * c;
+        }
+        out[((size_t)(t0 + j) * n_heads + kvh * R + r) * AT_D + dd] = __float2half_rn(gl > 0.0f ? ga / gl : 0.0f);
     }
 }
 
@@ -474,11 +607,25 @@ static int attention_launch(const void* qkv, void* kcache, void* vcache, const i
     __half* kc = reinterpret_cast<__half*>(kcache);
     __half* vc = reinterpret_cast<__half*>(vcache);
     __half* o = reinterpret_cast<__half*>(out);
-    // the arrival counters of the splits sit behind the partial results
-    unsigned int* counters = reinterpret_cast<unsigned int*>(scratch + (size_t)tokens * n_heads * nsplit * (AT_D + 2));
+    if (!inv_freq && nsplit == 1 && tokens_per_seq >= 8) {      // prefill: tokens of a sequence share K / V fetches
+        const int QB = 16 / R, nblk = (tokens_per_seq + QB - 1) / QB;
+        const dim3 bgrid((unsigned)((tokens / tokens_per_seq) * n_kv * nblk));
+#define SBVR_ATTB(RR)                                                                                               \
+    SBVR_CUDA_TRY(launch_pdl(attention_block_kernel<RR>, bgrid, dim3(128), 0, st, q, static_cast<const __half*>(kc), \
+                             static_cast<const __half*>(vc), positions, o, tokens_per_seq, n_heads, n_kv, max_ctx, scale))
+        switch (R) {
+            case 1: SBVR_ATTB(1); break;
+            case 2: SBVR_ATTB(2); break;
+            case 4: SBVR_ATTB(4); break;
+            case 8: SBVR_ATTB(8); break;
+            default: return SBVR_ERR_UNSUPPORTED;
+        }
+#undef SBVR_ATTB
+        return SBVR_OK;
+    }
 #define SBVR_ATT(RR)                                                                                              \
     SBVR_CUDA_TRY(launch_pdl(attention_kernel<RR>, grid, dim3(128), 0, st, q, kc, vc, positions, o, scratch,     \
-                             counters, tokens_per_seq, n_heads, n_kv, max_ctx, scale, nsplit, inv_freq, attn_scaling))
+                             tokens_per_seq, n_heads, n_kv, max_ctx, scale, nsplit, inv_freq, attn_scaling))
     switch (R) {
         case 1: SBVR_ATT(1); break;
         case 2: SBVR_ATT(2); break;
@@ -487,7 +634,9 @@ static int attention_launch(const void* qkv, void* kcache, void* vcache, const i
         default: return SBVR_ERR_UNSUPPORTED;
     }
 #undef SBVR_ATT
-
+    if (nsplit > 1)
+        SBVR_CUDA_TRY(launch_pdl(attention_combine_kernel, dim3(tokens * n_heads), dim3(128), 0, st,
+                                 static_cast<const float*>(scratch), o, nsplit));
     return SBVR_OK;
 }
 
