@@ -344,7 +344,8 @@ __global__ void __launch_bounds__(128) attention_block_kernel(const __half* __re
     pdl_launch_dependents();
     pdl_wait();
     const int nblk = (tokens_per_seq + QB - 1) / QB;
-    const int qblk = blockIdx.x % nblk, rest = blockIdx.x / nblk;
+    // the blocks with the longest context are scheduled first (they finish last otherwise)
+    const int rest = blockIdx.x % ((int)gridDim.x / nblk), qblk = nblk - 1 - (int)blockIdx.x / ((int)gridDim.x / nblk);
     const int kvh = rest % n_kv, seq = rest / n_kv;
     const int t0 = seq * tokens_per_seq + qblk * QB;
     const int nq = min(QB, tokens_per_seq - qblk * QB);
@@ -377,7 +378,7 @@ __global__ void __launch_bounds__(128) attention_block_kernel(const __half* __re
         for (int q = 0; q < NQ; ++q) sc[q] = 0.0f;
         if (p < P) {
             const uint4* kr = reinterpret_cast<const uint4*>(kb + (size_t)p * AT_D);
-#pragma unroll 2
+#pragma unroll 4
             for (int c = 0; c < AT_D / 8; ++c) {
                 const uint4 kv = __ldg(kr + c);
                 const __half2* kh = reinterpret_cast<const __half2*>(&kv);
