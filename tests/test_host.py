@@ -92,3 +92,28 @@ def test_no_cpu_fallback():
         sbvr.linear(torch.zeros((1, 256), dtype=torch.float16), w)
     with pytest.raises(RuntimeError):
         w.decode()
+
+
+def test_glue_and_fused_entry_points_validate_before_any_cuda_call():
+    from sbvr import _lib
+    L = _lib.lib
+    buf = (ctypes.c_uint32 * 64)()
+    p = ctypes.addressof(buf)
+    assert L.sbvr_add_rmsnorm_f16(None, None, p, None, p, 1, 4096, 1e-5, None) == -1
+    assert L.sbvr_add_rmsnorm_f16(p, None, p, None, p, 1, 4100, 1e-5, None) == -2          # hidden % 8
+    assert L.sbvr_add_rmsnorm_f16(p + 2, None, p, None, p, 1, 4096, 1e-5, None) == -3      # alignment
+    assert L.sbvr_rope_append_f16(p, p, p, 1.0, p, p, 3, 2, 4, 2, 128, 64, None) == -1     # tokens % tokens_per_seq
+    assert L.sbvr_attention_f16(p, p, p, p, p, None, 1, 1, 6, 4, 128, 64, 0.1, 1, None) == -1   # heads % kv heads
+    assert L.sbvr_attention_f16(p, p, p, p, p, None, 1, 1, 4, 2, 64, 64, 0.1, 1, None) == -7    # head_dim
+    assert L.sbvr_attention_f16(p, p, p, p, p, None, 1, 1, 4, 2, 128, 64, 0.1, 4, None) == -5   # splits need scratch
+    assert L.sbvr_rope_attention_f16(p, p, None, 1.0, p, p, p, None, 1, 4, 2, 128, 64, 0.1, 1, None) == -1
+    assert L.sbvr_silu_mul_f16(p, p, 1, 12, None) == -2
+    assert L.sbvr_embedding_f16(None, p, p, 1, 64, None) == -1
+    assert L.sbvr_argmax_f16(p, None, None, 1, 10, None) == -1
+    # fused linear: unknown op, bad packed arguments, missing workspace
+    assert L.sbvr_linear_fused_f16(7, p, None, None, None, 0.0, p, p, 1, p, 4, None, p, 1, 64, 256, 4, 256, None, None) == -1
+    assert L.sbvr_linear_fused_f16(1, p, None, None, None, 0.0, p, p, 1, p, 4, None, p, 1, 64, 300, 4, 256, None, None) == -2
+    assert L.sbvr_linear_fused_f16(1, p, None, None, None, 0.0, p, p, 1, p, 4, None, p, 1, 64, 256, 4, 256, None, None) == -5
+    assert L.sbvr_allreduce_add_rmsnorm_f16(p, p, p, 3, 0, 0, 2, 4096, p, p, p, p, 1, 4096, 1e-5, None, None) == -1
+    out = ctypes.c_size_t(0)
+    assert L.sbvr_workspace_bytes(0, 0, 64, 256, ctypes.byref(out)) == -1
