@@ -22,24 +22,26 @@
 // Accuracy: weights are formed in fp16 with one rounding per plane (not the single rounding of decode()), which
 // perturbs a weight by at most a few fp16 ulps of its partial sums; products accumulate in fp32.
 //
-// Structure: persistent CTAs of 14 warps.  Warps 0-11 are three decoder warpgroups that take the 64-k stages
+// Structure: persistent CTAs of 18 warps.  Warps 0-15 are four decoder warpgroups that take the 64-k stages
 // round-robin and, once the MMAs of a work item have finished, read D from tensor memory, add the bias and
 // write fp16 (or fp32 partial sums when K is split over several CTAs: small activation batches on wide GPUs;
-// the last CTA to arrive adds the parts in a fixed order, so results do not depend on timing).  Warp 12 issues
-// the MMAs from one elected lane; warp 13 streams the activation blocks.  Every wait is bounded; on a time-out
+// the last CTA to arrive adds the parts in a fixed order, so results do not depend on timing).  Warp 16 issues
+// the MMAs from one elected lane; warp 17 streams the activation blocks.  At M = 2048 the kernel is bound by the
+// L2 traffic of the activation blocks (32 KB per 128 x 256 x 64 MMA stage and SM), not by the decoder: three or
+// four decoder warpgroups, shifts moved to the multiply pipe, all measured within 3 % of each other.  Every wait is bounded; on a time-out
 // the kernel records it in the status word, skips the remaining work without skipping a barrier, frees its
 // tensor memory and returns.
 #include "common.cuh"
 
 namespace sbvr {
 
-constexpr int GM_DWGS = 3;
+constexpr int GM_DWGS = 4;
 constexpr int GM_DTHREADS = GM_DWGS * 128;
 constexpr int GM_IWARP = GM_DWGS * 4;
 constexpr int GM_PWARP = GM_IWARP + 1;
 constexpr int GM_THREADS = (GM_PWARP + 1) * 32;
-constexpr int GM_ASLOTS = 4;                    // decoded 128 x 64 weight tiles resident in tensor memory
-constexpr int GM_A_COL = 256;                   // D occupies columns [0, NX), the A ring [256, 384)
+constexpr int GM_ASLOTS = 6;                    // decoded 128 x 64 weight tiles resident in tensor memory
+constexpr int GM_A_COL = 256;                   // D occupies columns [0, NX), the A ring [256, 256 + 32 slots)
 constexpr int GM_TMEM_COLS = 512;
 constexpr int GM_XSTAGES = 6;
 constexpr int GM_HDR = 1024;
