@@ -213,7 +213,11 @@ __global__ void __launch_bounds__(GM_THREADS, 1) linear_gemm_kernel(const GmPara
         }
     } else if (warp == GM_IWARP) {
         // ------------------------------ MMA issuer ------------------------------
-        int it = 0, seq = 0;
+        // A barrier poll costs a couple of hundred cycles on a busy SM even when the phase is complete, and two polls
+        // per stage in front of four MMAs made this warp the kernel's serial bottleneck.  So the lanes poll the
+        // barriers of the next LOOK stages in one go and the warp issues every stage found complete.
+        constexpr int LOOK = GM_XSTAGES < GM_ASLOTS ? GM_XSTAGES : GM_ASLOTS;
+        int it = 0, seq = 0, ready = 0;            // stages [it, ready) are known to have both operands in place
         bool ok = true;
         for (int item = blockIdx.x; item < p.items && ok; item += grid, ++seq) {
             if (seq > 0) {                          // D of the previous item must have been read out
@@ -225,12 +229,29 @@ __global__ void __launch_bounds__(GM_THREADS, 1) linear_gemm_kernel(const GmPara
             }
             for (int ks = 0; ks < SPP; ++ks, ++it) {
                 const int st = it % GM_XSTAGES, slot = it % GM_ASLOTS;
-                if (flags[0] || !mbar_wait_async(&x_full[st], (uint32_t)(it / GM_XSTAGES) & 1u) ||
-                    !mbar_wait_timed(&a_full[slot], (uint32_t)(it / GM_ASLOTS) & 1u)) {
-                    ok = false;
-                    break;
+                if (it >= ready) {
+                    long long t0 = 0;
+                    for (;;) {
+                        const int s = it + lane;   // lane l looks at stage it + l
+                        bool okl = false;
+                        if (lane < LOOK)
+                            okl = mbar_test(&x_full[s % GM_XSTAGES], (uint32_t)(s / GM_XSTAGES) & 1u) &&
+                                  mbar_test(&a_full[s % GM_ASLOTS], (uint32_t)(s / GM_ASLOTS) & 1u);
+                        const uint32_t mask = __ballot_sync(0xffffffffu, okl);
+                        const int n = __ffs((int)~mask) - 1;       // stages complete in a row, starting at `it`
+                        if (n > 0) {
+                            ready = it + n;
+                            break;
+                        }
+                        if (t0 == 0) t0 = clock64();
+                        else if (flags[0] || clock64() - t0 > 2000000000LL) {
+                            ok = false;
+                            break;
+                        }
+                    }
+                    if (!ok) break;
+                    gm_fence_after();
                 }
-                gm_fence_after();
                 const uint32_t bs = smem_u32(xs + (size_t)st * STAGE_BYTES);
                 if (elect_one()) {
 #pragma unroll
