@@ -26,9 +26,9 @@
 // round-robin and, once the MMAs of a work item have finished, read D from tensor memory, add the bias and
 // write fp16 (or fp32 partial sums when K is split over several CTAs: small activation batches on wide GPUs;
 // the last CTA to arrive adds the parts in a fixed order, so results do not depend on timing).  Warp 16 issues
-// the MMAs from one elected lane; warp 17 streams the activation blocks.  At M = 2048 the kernel is bound by the
-// L2 traffic of the activation blocks (32 KB per 128 x 256 x 64 MMA stage and SM), not by the decoder: three or
-// four decoder warpgroups, shifts moved to the multiply pipe, all measured within 3 % of each other.  Every wait is bounded; on a time-out
+// the MMAs from one elected lane; warp 17 streams the activation blocks.  At M = 2048 the tensor pipe is busy about
+// half of the time: a stage costs the decoders about 630 issue slots per scheduler against 512 tensor cycles, and
+// the serial work of the issuer warp (barrier polls, four MMAs, three commits per stage) sits on the same path.  Every wait is bounded; on a time-out
 // the kernel records it in the status word, skips the remaining work without skipping a barrier, frees its
 // tensor memory and returns.
 #include "common.cuh"
