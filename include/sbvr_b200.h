@@ -121,6 +121,15 @@ SBVR_API int sbvr_linear_f16_noalloc(const void* x, const uint32_t* bvr, const v
                                      const void* coeff, int C, const void* bias, void* y, int M, int N, int K, int S,
                                      int G, sbvr_stream_t stream);
 
+/* y[M, N] = fp16( sum_g sum_{a,b} popc(l_a & r_b) * cl[g,m,a] * cr[g,n,b] + bias ): both operands SBVR-encoded (group
+ * length 256), l_bvr uint32 [K/32, M, LS], l_idx uint8|uint16 [K/256, M], l_cache fp16 [Cl, LS]; r_* likewise with N, RS.
+ * LS, RS in {2, 3, 4}.  Replaces `_sbvr_mm_T(l_bvr, l_coeff_idx, l_coeff_cache, r_bvr, r_coeff_idx, r_coeff_cache, bias)`
+ * (sbvr/kernels/sbvr_ops.cpp:35-76 -> launch_cuda_sbvr_mm_T, sbvr/kernels/sbvr_kernel.cu:914-1023, kernel :464-562), with
+ * exact popcounts (the reference's 8-bit counters wrap at 256) and fp32 coefficient products (the reference uses half2). */
+SBVR_API int sbvr_popc_mm_f16(const uint32_t* l_bvr, const void* l_idx, int l_idx_bytes, const void* l_cache, int Cl, int LS,
+                              const uint32_t* r_bvr, const void* r_idx, int r_idx_bytes, const void* r_cache, int Cr, int RS,
+                              const void* bias, void* y, int M, int N, int K, sbvr_stream_t stream);
+
 /* ---- the kernels between the linears of a Llama decoder layer ----------------------------------------------
  * Each replaces a chain of eager PyTorch ops of the reference model (models/sbvr_llama.py) by one launch.
  * All tensors fp16, contiguous, 16-byte aligned unless noted. */

@@ -162,6 +162,30 @@ def linear_f64(x, bvr, coeff_idx, coeff, bias=None, G: int = 256) -> np.ndarray:
     return y
 
 
+# --------------------------------------------------------------------------
+# SBVR x SBVR (both operands encoded)
+# --------------------------------------------------------------------------
+def popc_mm_f64(l_bvr, l_idx, l_coeff, r_bvr, r_idx, r_coeff, bias=None) -> np.ndarray:
+    """y[m, n] = sum_g sum_{a,b} popc(l_a & r_b) c^l_a c^r_b (+ bias) in float64, group length 256.
+
+    The quantity `cuda_1xtN_sbvr_mm_T` / `simd_kernel_1xN_popc_first` of the reference compute
+    (sbvr/kernels/sbvr_kernel.cu:464-562, sbvr/kernels/sbvr_kernel.cpp:251-399) -- with exact popcounts
+    (the reference's 8-bit counters wrap at 256) and no half-precision products.  popc(l_a & r_b) over a group
+    is the inner product of the two 0/1 bit vectors, so the sum over planes and groups is the product of the two
+    operands decoded WITHOUT rounding: that is how it is formed here.
+    """
+    def exact(bvr, idx, coeff):
+        bits = unpack_bvr(bvr).astype(np.float64)                  # [R, K, S]
+        c = group_coeffs(idx, coeff).astype(np.float64)            # [K/256, R, S]
+        R, K, S = bits.shape
+        cs = np.repeat(c.transpose(1, 0, 2), 256, axis=1)          # [R, K, S]
+        return (bits * cs).sum(-1)                                 # [R, K]
+    y = exact(l_bvr, l_idx, l_coeff) @ exact(r_bvr, r_idx, r_coeff).T
+    if bias is not None and np.size(bias) > 0:
+        y = y + np.asarray(bias, dtype=np.float16).astype(np.float64)[None, :]
+    return y
+
+
 def max_rel_err(y, ref) -> float:
     """The tolerance metric of the parity tests: max|y - ref| / max|ref|."""
     y = np.asarray(y).astype(np.float64)

@@ -706,6 +706,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) linear_tc_kernel(const TcParams
         const int wpos = (S == 3) ? 3 * (lane >> 2) + (lane & 3) : lane;
         for (int ti = 0; ti < n_tiles; ++ti) {
             TC_PROF(0);
+            // The state of the MMA barrier of tile ti-2 is requested before the copies of tile ti+3 are issued and
+            // looked at after them: a barrier poll costs a couple of hundred cycles on a busy SM even when the phase is
+            // complete, and this way that latency hides behind the copy requests (measured: -5.6 % at 14336 x 4096).
+            const int db_e = (dmod == 2) ? 0 : dmod + 1;
+            bool early = false;
+            if (PIPE && ti >= 2 && !dead) early = mbar_test(&mma_bar[wg * 3 + db_e], (mph >> db_e) & 1u);
             load_tile();                           // tile ti + 3
             const int abuf = PIPE ? (ti & 1) : 0;
             TC_PROF(1);
@@ -714,7 +720,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) linear_tc_kernel(const TcParams
             // buffer `abuf`, which those MMAs read.
             if (PIPE && ti >= 2) {
                 const int db = (dmod == 2) ? 0 : dmod + 1;
-                wait_mma(db);
+                early = __all_sync(0xffffffffu, early);
+                if (early) {
+                    mph ^= 1u << db;
+                    tc_fence_after();
+                } else {
+                    wait_mma(db);
+                }
                 if (!dead) epilogue(db, s2);
                 if (last2) deposit(ui2);
             }

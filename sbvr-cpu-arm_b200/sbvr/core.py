@@ -336,11 +336,36 @@ def linear_fused(op: int, x: torch.Tensor, w: sbvr, out: torch.Tensor, delta: Op
     return True
 
 
+@torch.inference_mode()
 def mm_T(lhs, rhs: sbvr, bias=None):
-    """`lhs @ rhs.T + bias` (reference `mm_T`, sbvr/core.py:1029-1039).  `lhs` may be an fp16 tensor or, as in
-    the reference, an `sbvr` object, which is decoded on the GPU first."""
-    x = lhs.decode() if isinstance(lhs, sbvr) else lhs
-    return linear(x, rhs, bias)
+    """`lhs @ rhs.T + bias` (reference `mm_T`, sbvr/core.py:1029-1039).  `lhs` may be an fp16 tensor (-> `linear`) or, as
+    in the reference, an `sbvr` object: then both operands stay encoded and the product runs on the popcount kernel
+    (`sbvr_popc_mm_f16`, the reference's `_sbvr_mm_T`); encodings it does not cover (more than 4 planes, direct
+    coefficients, group length other than 256) are decoded on the GPU and go through `linear`."""
+    if not isinstance(lhs, sbvr):
+        return linear(lhs, rhs, bias)
+    ok = (lhs.bvr_len == 256 and rhs.bvr_len == 256 and lhs.coeff_idx is not None and rhs.coeff_idx is not None and
+          2 <= lhs.num_sums <= 4 and 2 <= rhs.num_sums <= 4 and lhs.in_features_padded == rhs.in_features_padded and
+          lhs.bvr.device == rhs.bvr.device)
+    if not ok:
+        return linear(lhs.decode(), rhs, bias)
+    dev = rhs.bvr.device
+    di = _cuda_index(dev)
+    M, N, K = lhs.out_features, rhs.out_features, rhs.in_features_padded
+    if bias is not None and bias.numel() == 0:
+        bias = None
+    if bias is not None:
+        if bias.numel() != N or bias.dtype != torch.float16:
+            raise ValueError("bias must be float16 of length N")
+        bias = bias.contiguous()
+    y = torch.empty((M, N), dtype=torch.float16, device=dev)
+    lb, lix, lib_, lc, lC = lhs._abi_args()
+    rb, rix, rib, rc, rC = rhs._abi_args()
+    with torch.cuda.device(di):
+        st = torch.cuda.current_stream().cuda_stream
+        _lib.check(_lib.lib.sbvr_popc_mm_f16(lb, lix, lib_, lc, lC, lhs.num_sums, rb, rix, rib, rc, rC, rhs.num_sums,
+                                             _ptr(bias), y.data_ptr(), M, N, K, st), "sbvr_popc_mm_f16")
+    return y
 
 
 def load(filename, device=None, verbose_level=1, cpu_kernel=False, cpu_kernel_v2=False) -> sbvr:

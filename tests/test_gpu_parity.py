@@ -311,3 +311,23 @@ def test_fused_add_rmsnorm_linear(M, with_delta):
     assert torch.equal(h_out, h_sep)
     assert ((y.float() - y_sep.float()).abs().max() / y_sep.float().abs().max()).item() < 2e-3
     check_status()
+
+
+@pytest.mark.parametrize("LS,RS", [(2, 2), (4, 4), (3, 4), (4, 2), (2, 3)])
+@pytest.mark.parametrize("M", [1, 3, 11])
+def test_popcount_mm_T_both_operands_encoded(LS, RS, M):
+    """`sbvr.mm_T(lhs_sbvr, rhs_sbvr, bias)` on the popcount kernel against the exact product of the two encodings,
+    and against the reference's comparator for this kernel, decode(a) @ decode(b).T + bias (test_sbvr.py:321-325)."""
+    import sbvr
+    N, K = 328, 1024
+    pl = O.make_packed(M, K, LS, G=256, mode="u8", seed=100 + LS * 10 + M)
+    pr = O.make_packed(N, K, RS, G=256, mode="u16", C=512, seed=200 + RS)
+    a, b = to_sbvr(pl), to_sbvr(pr)
+    rng = np.random.default_rng(M)
+    bias = (rng.standard_normal(N) * 0.05).astype(np.float16)
+    y = h2n(sbvr.mm_T(a, b, torch.from_numpy(bias).cuda())).astype(np.float64)
+    ref = O.popc_mm_f64(pl["bvr"], pl["coeff_idx"], pl["coeff"], pr["bvr"], pr["coeff_idx"], pr["coeff"], bias)
+    assert np.abs(y - ref).max() / np.abs(ref).max() <= 2e-3
+    dense = O.linear_from_dense(O.decode(pl["bvr"], pl["coeff_idx"], pl["coeff"]),
+                                O.decode(pr["bvr"], pr["coeff_idx"], pr["coeff"]), bias).astype(np.float64)
+    assert np.abs(y - dense).max() / np.abs(dense).max() <= TOL

@@ -113,3 +113,24 @@ def test_float_half_roundtrip_tables():
         expect = (np.float32(0.0) + chunk.astype(np.float32)).astype(np.float16)   # 0 + (-0) = +0
         assert np.array_equal(_bits(W[:, 0]), _bits(expect))
     assert lib.sbvr_oracle_threads() >= 1
+
+
+def test_popcount_product_oracle_matches_its_definition():
+    """`popc_mm_f64` (formed as a product of unrounded decodes) against the popcount sum written out."""
+    pl = O.make_packed(3, 512, 4, G=256, mode="u8", seed=1)
+    pr = O.make_packed(40, 512, 3, G=256, mode="u16", C=512, seed=2)
+    y = O.popc_mm_f64(pl["bvr"], pl["coeff_idx"], pl["coeff"], pr["bvr"], pr["coeff_idx"], pr["coeff"])
+    bl, br = O.unpack_bvr(pl["bvr"]), O.unpack_bvr(pr["bvr"])
+    cl = O.group_coeffs(pl["coeff_idx"], pl["coeff"]).astype(np.float64)
+    cr = O.group_coeffs(pr["coeff_idx"], pr["coeff"]).astype(np.float64)
+    for m, n in [(0, 0), (1, 17), (2, 39)]:
+        s = 0.0
+        for g in range(2):
+            for a in range(4):
+                for b in range(3):
+                    pc = int((bl[m, g * 256:(g + 1) * 256, a] & br[n, g * 256:(g + 1) * 256, b]).sum())
+                    s += pc * cl[g, m, a] * cr[g, n, b]
+        assert abs(s - y[m, n]) < 1e-12
+    dense = O.linear_from_dense(O.decode(pl["bvr"], pl["coeff_idx"], pl["coeff"]),
+                                O.decode(pr["bvr"], pr["coeff_idx"], pr["coeff"])).astype(np.float64)
+    assert np.abs(y - dense).max() / np.abs(dense).max() < 2e-3
