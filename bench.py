@@ -450,8 +450,31 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def decode_step_case():
+    """One eager decode step (batch 1, context 512) of a 4-layer model with Llama-3-8B layer shapes, inside the NVTX
+    range "decode", after a prefill and two warm-up steps."""
+    import torch
+    from models.sbvr_llama import LlamaConfig, SBVRLlamaForCausalLM
+    cfg = LlamaConfig.preset("8b")
+    cfg.num_hidden_layers = 4
+    m = SBVRLlamaForCausalLM(cfg, max_batch=1, max_ctx=600).init_synthetic(7)
+    ids = torch.randint(0, cfg.vocab_size, (1, 512), device="cuda", generator=torch.Generator(device="cuda").manual_seed(99))
+    nxt = m.prefill(ids)
+    pos = torch.full((1,), 512, dtype=torch.int32, device="cuda")
+    for _ in range(2):
+        m.decode_step(nxt, pos)
+    torch.cuda.synchronize()
+    torch.cuda.nvtx.range_push("decode")
+    m.decode_step(nxt, pos)
+    torch.cuda.synchronize()
+    torch.cuda.nvtx.range_pop()
+    print(json.dumps({"kernel_case": "decode_step", "layers": 4, "context": 512}))
+
+
 def kernel_case(which):
     """Six 14336 x 4096 weights (176 MB, more than L2), two warm-up rounds, then one launch per weight."""
+    if which == "decode_step":
+        return decode_step_case()
     import torch
     import sbvr
     dev = torch.device("cuda", 0)
@@ -482,8 +505,9 @@ def main():
     ap.add_argument("--no-extras", action="store_true",
                     help="only the headline GEMV measurement (no M sweep, prefill GEMM or Llama decode sections)")
     ap.add_argument("--skip-70b", action="store_true", help="leave the 70B decode out of the Llama section")
-    ap.add_argument("--kernel-case", default=None, choices=["gemv", "gemm16", "gemm2048"],
-                    help="run a few launches of one kernel on 14336x4096 weights and exit (for profilers)")
+    ap.add_argument("--kernel-case", default=None, choices=["gemv", "gemm16", "gemm2048", "decode_step"],
+                    help="run a few launches of one kernel on 14336x4096 weights, or one eager decode step of a "
+                         "4-layer Llama-3-8B-shaped model inside the NVTX range 'decode', and exit (for profilers)")
     args = ap.parse_args()
     if args.kernel_case:
         return kernel_case(args.kernel_case)
