@@ -331,3 +331,21 @@ def test_popcount_mm_T_both_operands_encoded(LS, RS, M):
     dense = O.linear_from_dense(O.decode(pl["bvr"], pl["coeff_idx"], pl["coeff"]),
                                 O.decode(pr["bvr"], pr["coeff_idx"], pr["coeff"]), bias).astype(np.float64)
     assert np.abs(y - dense).max() / np.abs(dense).max() <= TOL
+
+
+@pytest.mark.parametrize("shape", [(128256, 4096), (6144, 4096), (28672, 4096), (8192, 8192), (10240, 8192), (8192, 28672)])
+def test_linear_model_shapes_m1(shape):
+    """The shapes the Llama models actually launch at batch 1: lm_head, fused q|k|v and gate|up of the 8B model, and
+    hidden / fused q|k|v / down of the 70B model (many row tiles per CTA, long K)."""
+    import sbvr
+    N, K = shape
+    p = O.make_packed(N, K, 4, G=256, mode="u16", C=4096, seed=N % 97)
+    w = to_sbvr(p)
+    rng = np.random.default_rng(K)
+    x = rng.standard_normal((1, K)).astype(np.float16)
+    ref = O.linear_c(x, p["bvr"], p["coeff_idx"], p["coeff"], G=256)
+    y = h2n(sbvr.linear(torch.from_numpy(x).cuda(), w, None, algo=2))
+    err = O.max_rel_err(y, ref)
+    assert err <= TOL, err
+    assert err <= 2e-3, err
+    check_status()
