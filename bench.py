@@ -3,7 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
-Workload (BASELINE config 1 at its headline point): one STEP = the seven SBVR linears of a
+Workload (the GEMV / small-M sweep configuration at its headline point): one STEP = the seven SBVR linears of a
 Llama-3-8B decoder layer at batch 1 -- q, o (4096x4096), k, v (1024x4096), gate, up (14336x4096),
 down (4096x14336) -- 4 bit-planes, group 256, uint16 codebook of 4096 lines, fp16 activations.
 Weights are seeded synthetic packed tensors in the reference layout (Bernoulli(0.5) planes,
@@ -303,7 +303,7 @@ def graph_time_us(torch, stream, fns, reps=5):
 
 
 def small_m_and_prefill(torch, dev, stream):
-    """BASELINE configs 1 and 2 beside the headline: the M sweep of the layer shapes (HBM roofline) and the
+    """The two neighbouring configurations beside the headline: the M sweep of the layer shapes (HBM roofline) and the
     M = 2048 prefill GEMM (tensor roofline).  Every timing cycles through more weights than L2 holds."""
     import sbvr
     peak, _ = measured_peak()

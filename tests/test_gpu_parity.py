@@ -104,7 +104,7 @@ def test_linear_grid(S, G, mode, M, algo):
 @pytest.mark.parametrize("shape", [(4096, 4096), (1024, 4096), (14336, 4096), (4096, 14336)])
 @pytest.mark.parametrize("S", [2, 3, 4])
 def test_linear_llama_shapes_m1(shape, S):
-    """BASELINE config 1 shapes at M=1, codebook u16, G=256, both kernels against the threaded C oracle."""
+    """The four Llama-3-8B layer shapes at M=1, codebook u16, G=256, both kernels against the threaded C oracle."""
     import sbvr
     N, K = shape
     p = O.make_packed(N, K, S, G=256, mode="u16", C=4096, seed=7)
