@@ -36,13 +36,13 @@ __device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) 
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-__global__ void __launch_bounds__(256) allreduce_add_rmsnorm_kernel(
+__global__ void __launch_bounds__(1024) allreduce_add_rmsnorm_kernel(
     const unsigned long long* __restrict__ peer_bufs,    // [world] base address of every rank's buffer area
     const unsigned long long* __restrict__ peer_flags,   // [world] base address of every rank's flag array
     const int* __restrict__ step_ptr, int calls_per_step, int call_idx, int rank, int world, size_t buf_elems,
     const __half* h_in, const __half* __restrict__ weight, __half* h_out, __half* __restrict__ y, int hidden, float eps,
     unsigned int* status) {
-    __shared__ float red[8];
+    __shared__ float red[32];
     __shared__ int ok_s;
     pdl_launch_dependents();
     pdl_wait();                                    // the partial of this rank (previous kernel) is complete from here on
@@ -78,14 +78,26 @@ __global__ void __launch_bounds__(256) allreduce_add_rmsnorm_kernel(
         float acc[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) acc[e] = 0.0f;
-        for (int r = 0; r < world; ++r) {
-            const __half* src = reinterpret_cast<const __half*>(peer_bufs[r]) + parity_off + row + (size_t)i * 8;
-            const uint4 v = __ldcv(reinterpret_cast<const uint4*>(src));
-            const __half2* vh = reinterpret_cast<const __half2*>(&v);
+        // the loads of up to eight ranks are all issued before the first is used: one NVLink round trip per batch,
+        // not one per rank; the sum still runs in rank order
+        for (int r0 = 0; r0 < world; r0 += 8) {
+            uint4 v[8];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const float2 f = __half22float2(vh[e]);
-                acc[2 * e] += f.x, acc[2 * e + 1] += f.y;
+            for (int u = 0; u < 8; ++u) {
+                const int r = (r0 + u < world) ? r0 + u : rank;
+                const __half* src = reinterpret_cast<const __half*>(peer_bufs[r]) + parity_off + row + (size_t)i * 8;
+                v[u] = __ldcv(reinterpret_cast<const uint4*>(src));
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                if (r0 + u < world) {
+                    const __half2* vh = reinterpret_cast<const __half2*>(&v[u]);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float2 f = __half22float2(vh[e]);
+                        acc[2 * e] += f.x, acc[2 * e + 1] += f.y;
+                    }
+                }
             }
         }
         uint4 a = *reinterpret_cast<const uint4*>(h_in + row + (size_t)i * 8);
@@ -103,8 +115,7 @@ __global__ void __launch_bounds__(256) allreduce_add_rmsnorm_kernel(
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
     __syncthreads();
     float tot = 0.0f;
-#pragma unroll
-    for (int w = 0; w < 8; ++w) tot += red[w];
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) tot += red[w];
     const float rs = rsqrtf(tot / (float)hidden + eps);
     for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
         const uint4 a = *reinterpret_cast<const uint4*>(h_out + row + (size_t)i * 8);     // written above by this thread
@@ -139,7 +150,7 @@ extern "C" int sbvr_allreduce_add_rmsnorm_f16(const void* peer_bufs_dev, const v
     if ((reinterpret_cast<uintptr_t>(h_in) | reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(h_out) |
          reinterpret_cast<uintptr_t>(y)) & 15)
         return SBVR_ERR_ALIGN;
-    SBVR_CUDA_TRY(launch_pdl(allreduce_add_rmsnorm_kernel, dim3(rows), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
+    SBVR_CUDA_TRY(launch_pdl(allreduce_add_rmsnorm_kernel, dim3(rows), dim3(hidden >= 8192 ? 1024 : 512), 0, reinterpret_cast<cudaStream_t>(stream),
                              reinterpret_cast<const unsigned long long*>(peer_bufs_dev),
                              reinterpret_cast<const unsigned long long*>(peer_flags_dev), step_dev, calls_per_step, call_idx,
                              rank, world, buf_elems, reinterpret_cast<const __half*>(h_in),
