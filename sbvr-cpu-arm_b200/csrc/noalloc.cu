@@ -8,9 +8,9 @@
 // in global mode, where an allocation call would break that capture.  Such callers cannot create
 // the `sbvr_workspace_t` the regular entry point wants, because creating it is a cudaMalloc.
 //
-// What it does instead.  The scratch the kernels need (time-out status word, split-K arrival
-// counters, fp32 partial sums, the quantised activation digits) lives in ONE fixed array that is
-// part of this library's device image, `g_noalloc_scratch` below: SBVR_NOALLOC_BYTES = 4 MiB per
+// What it does instead.  The scratch the kernels need (the time-out status word and the arrival
+// counters today; the array is sized for kernels that also keep partial sums there) lives in ONE
+// fixed array that is part of this library's device image, `g_noalloc_scratch` below: SBVR_NOALLOC_BYTES = 4 MiB per
 // GPU that loads the library, held until the process exits.  Nothing is allocated or freed here,
 // by this file or by anything it calls.
 //
@@ -23,9 +23,8 @@
 //     may load the module) and sets the kernels' shared-memory attribute.  Make that first call
 //     outside any stream capture, with the device current; later calls only enqueue work.
 //   * A problem whose scratch does not fit is refused with SBVR_ERR_NOALLOC_LIMIT before anything is
-//     launched.  Roughly: ceil(N/32) * 128 * M * (contributors per row tile) bytes of partial sums
-//     plus K/256 * M KiB of digits must stay under 4 MiB; every Llama-3 8B/70B layer shape at
-//     M <= 4 fits, a 128 256-row vocabulary projection fits up to M = 3.
+//     launched.  The decode kernel (M <= 4) keeps its sums and the quantised activations on the SM, so
+//     every shape it serves fits; shapes it does not serve run on the SIMT kernel, which needs no scratch.
 //   * A time-out of a bounded device wait is recorded in the array but this entry point has no
 //     synchronising call to report it; use the workspace form if you need that.
 #include <mutex>
