@@ -319,7 +319,7 @@ def small_m_and_prefill(torch, dev, stream):
         idx = torch.randint(0, C, (K // G, N), device=dev, generator=gen).to(torch.int16).view(torch.uint16)
         cache = (torch.randn((C, S), device=dev, generator=gen) * 0.01).half()
         return sbvr.sbvr.from_packed(bvr, idx, cache, group_len=G, device=dev)
-    sweep, prefill = [], []
+    sweep, prefill, rowdeq = [], [], []
     for N, K in [(4096, 4096), (1024, 4096), (14336, 4096), (4096, 14336)]:
         ncopy = int(2 * 126e6 / (N * K * S / 8)) + 2
         ws_ = [mk(N, K) for _ in range(ncopy)]
@@ -338,7 +338,16 @@ def small_m_and_prefill(torch, dev, stream):
             prefill.append({"N": N, "K": K, "M": M, "us": round(us, 1), "TFLOPs": round(tf, 1),
                             "frac_of_measured_bf16_burst": round(tf / tf_peak, 4)})
         del ws_
-    return {"small_m_sweep": {"S": S, "G": G, "rows": sweep}, "prefill_gemm": prefill}
+        # the same product on the transposed ("row-dequant") encoding: packed W^T, groups along the output dimension
+        wt_ = [mk(K, N) for _ in range(ncopy)]
+        for M in (1, 4):
+            x = torch.randn((M, K), device=dev, generator=gen).half()
+            us = graph_time_us(torch, stream, [(lambda w=w: sbvr.row_deq_mm_T(x, w)) for w in wt_])
+            gbs = alg_bytes(M, N, K) / us / 1e3
+            rowdeq.append({"N": N, "K": K, "M": M, "us": round(us, 2), "GBps": round(gbs, 1), "frac": round(gbs / peak, 4)})
+        del wt_
+    return {"small_m_sweep": {"S": S, "G": G, "rows": sweep}, "prefill_gemm": prefill,
+            "row_deq_transposed_layout": {"S": S, "G": G, "rows": rowdeq}}
 
 
 def llama_decode(torch, dev, dist, world, preset, batch, prompt, new_tokens):

@@ -130,6 +130,18 @@ SBVR_API int sbvr_popc_mm_f16(const uint32_t* l_bvr, const void* l_idx, int l_id
                               const uint32_t* r_bvr, const void* r_idx, int r_idx_bytes, const void* r_cache, int Cr, int RS,
                               const void* bias, void* y, int M, int N, int K, sbvr_stream_t stream);
 
+/* y[M, N] = fp16(x[M, K] . W^T + bias) with the weight in the TRANSPOSED ("row-dequant") encoding, i.e. the packed tensors of
+ * `sbvr(W, trans=True)` (sbvr/core.py:244-245), whose groups of G run along the output dimension:
+ * bvr_t uint32 [N/32, K, S] (bit n % 32 of word (n / 32, k, s)), coeff_idx uint8|uint16 [N/G, K], coeff fp16 [C, S].
+ * Replaces `_sbvr_row_deq_mm_T(l_w, r_bvr, r_coeff_idx, r_coeff_cache, bias, use_shfl)` (sbvr/kernels/sbvr_ops.cpp:79-120 ->
+ * launch_cuda_sbvr_row_deq_mm_T, sbvr/kernels/sbvr_kernel.cu:876-912; kernels :121-359) for any M: same arithmetic (fp32 sum of
+ * the selected coefficients, fp32 products and sums, bias added in fp32, one conversion), deterministic.  N is the padded
+ * output length (a multiple of G, like the reference's `r_bvr.size(0) * 32`); S in {2, 3, 4}; idx_bytes in {1, 2}.
+ * Needs a workspace (partial sums when K is split over blocks). */
+SBVR_API int sbvr_linear_t_f16(const void* x, const uint32_t* bvr_t, const void* coeff_idx, int idx_bytes, const void* coeff,
+                               int C, const void* bias, void* y, int M, int N, int K, int S, int G, sbvr_workspace_t* ws,
+                               sbvr_stream_t stream);
+
 /* ---- the kernels between the linears of a Llama decoder layer ----------------------------------------------
  * Each replaces a chain of eager PyTorch ops of the reference model (models/sbvr_llama.py) by one launch.
  * All tensors fp16, contiguous, 16-byte aligned unless noted. */

@@ -186,6 +186,29 @@ def popc_mm_f64(l_bvr, l_idx, l_coeff, r_bvr, r_idx, r_coeff, bias=None) -> np.n
     return y
 
 
+# --------------------------------------------------------------------------
+# transposed ("row-dequant") weight encoding
+# --------------------------------------------------------------------------
+def linear_t_f64(x, bvr_t, coeff_idx, coeff, bias=None, G: int = 256, rounded: bool = False) -> np.ndarray:
+    """y = x @ W^T (+ bias) in float64 for a weight encoded TRANSPOSED (`sbvr(W, trans=True)`, sbvr/core.py:244-245):
+    the packed tensors describe the matrix W^T [K, N], i.e. bvr_t uint32 [N/32, K, S], coeff_idx [N/G, K].
+
+    `cuda_row_deq_mm_T` (sbvr/kernels/sbvr_kernel.cu:121-191) multiplies the activation by the fp32 sum of the selected
+    coefficients, NOT rounded to fp16 (`rounded=False`, the default here); `x @ w_t.decode()` is the same product with
+    every element rounded to fp16 first (`rounded=True`), the comparator the reference's scripts use for their kernels
+    (test_sbvr.py:321-325)."""
+    if rounded:
+        Wt = decode(bvr_t, coeff_idx, coeff, G=G).astype(np.float64)          # [K, N]
+    else:
+        bits = unpack_bvr(bvr_t).astype(np.float64)                            # [K, N, S]
+        c = group_coeffs(coeff_idx, coeff).astype(np.float64)                  # [N/G, K, S]
+        Wt = (bits * np.repeat(c.transpose(1, 0, 2), G, axis=1)).sum(-1)       # [K, N]
+    y = np.asarray(x, dtype=np.float16).astype(np.float64) @ Wt
+    if bias is not None and np.size(bias) > 0:
+        y = y + np.asarray(bias, dtype=np.float16).astype(np.float64)[None, :]
+    return y
+
+
 def max_rel_err(y, ref) -> float:
     """The tolerance metric of the parity tests: max|y - ref| / max|ref|."""
     y = np.asarray(y).astype(np.float64)

@@ -368,6 +368,17 @@ def mm_T(lhs, rhs: sbvr, bias=None):
     return y
 
 
+def row_deq_mm_T(x: torch.Tensor, w_t: sbvr, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """`x @ W.T + bias` for a weight encoded transposed (`sbvr(W, trans=True)` in the reference, sbvr/core.py:244-245:
+    `w_t` holds W^T, so `w_t.decode()` is [K, N]).  What the reference's `_sbvr_row_deq_mm_T` call sites compute
+    (test_sbvr.py:588-592); the result has the padded width `w_t.in_features_padded`, as there."""
+    from . import sbvr_cuda
+    if w_t.coeff_idx is None:
+        raise ValueError(_r_str("the transposed layout needs codebook indices (the reference has no direct form)"))
+    return sbvr_cuda._sbvr_row_deq_mm_T(x.reshape(-1, x.shape[-1]), w_t.bvr, w_t.coeff_idx, w_t.coeff_cache,
+                                        bias if bias is not None else w_t._get_dummy_bias(), 0)
+
+
 def load(filename, device=None, verbose_level=1, cpu_kernel=False, cpu_kernel_v2=False) -> sbvr:
     """Read a file written by `sbvr.save` here or by the reference (sbvr/core.py:1041-1050)."""
     ser = torch.load(filename)      # `_sbvr_serialized` is allow-listed in the package __init__

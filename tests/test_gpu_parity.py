@@ -349,3 +349,51 @@ def test_linear_model_shapes_m1(shape):
     assert err <= TOL, err
     assert err <= 2e-3, err
     check_status()
+
+
+@pytest.mark.parametrize("S", [2, 3, 4])
+@pytest.mark.parametrize("mode", ["u8", "u16"])
+@pytest.mark.parametrize("M", [1, 2, 3, 4, 7])
+def test_row_deq_mm_T_transposed_encoding(S, mode, M):
+    """`sbvr.sbvr_cuda._sbvr_row_deq_mm_T(x, bvr, idx, cache, bias, use_shfl)` on the transposed encoding (groups of 256
+    along the OUTPUT dimension) against the reference kernel's arithmetic (unrounded dequantised elements) and against
+    x @ w_t.decode() + bias, the comparator of the reference's scripts.  K = 800 is not a multiple of the block's 256."""
+    import sbvr
+    N, K = 512, 800
+    p = O.make_packed(K, N, S, G=256, mode=mode, seed=300 + S)          # packed W^T: K rows, N along the bits
+    w_t = to_sbvr(p)
+    rng = np.random.default_rng(7 * M + S)
+    x = rng.standard_normal((M, K)).astype(np.float16)
+    bias = (rng.standard_normal(N) * 0.05).astype(np.float16)
+    y = h2n(sbvr.sbvr_cuda._sbvr_row_deq_mm_T(torch.from_numpy(x).cuda(), w_t.bvr, w_t.coeff_idx, w_t.coeff_cache,
+                                              torch.from_numpy(bias).cuda(), 0)).astype(np.float64)
+    ref = O.linear_t_f64(x, p["bvr"], p["coeff_idx"], p["coeff"], bias)
+    assert y.shape == (M, N)
+    assert np.abs(y - ref).max() / np.abs(ref).max() <= 2e-3
+    dec = O.linear_t_f64(x, p["bvr"], p["coeff_idx"], p["coeff"], bias, rounded=True)
+    assert np.abs(y - dec).max() / np.abs(dec).max() <= TOL
+    # no bias = a tensor whose length is not N; the wrapper on the container gives the same numbers
+    y0 = sbvr.row_deq_mm_T(torch.from_numpy(x).cuda(), w_t)
+    y1 = sbvr.sbvr_cuda._sbvr_row_deq_mm_T(torch.from_numpy(x).cuda(), w_t.bvr, w_t.coeff_idx, w_t.coeff_cache,
+                                           w_t._get_dummy_bias(), 1)
+    assert torch.equal(y0, y1)
+    ref0 = O.linear_t_f64(x, p["bvr"], p["coeff_idx"], p["coeff"])
+    assert np.abs(h2n(y0).astype(np.float64) - ref0).max() / np.abs(ref0).max() <= 2e-3
+    check_status()
+
+
+@pytest.mark.parametrize("shape", [(4096, 4096), (1024, 4096), (14336, 4096), (4096, 14336)])
+def test_row_deq_mm_T_llama_shapes_deterministic(shape):
+    """Layer shapes (N x K) of Llama-3-8B at M = 1: the decoded transposed weight is the transpose of a decoded plain one,
+    so the product must agree with `x @ decode().T` computed on the GPU; K is split over blocks here, and two runs give
+    the same bits."""
+    import sbvr
+    N, K = shape
+    p = O.make_packed(K, N, 4, G=256, mode="u16", C=4096, seed=11)
+    w_t = to_sbvr(p)
+    x = torch.randn(1, K, dtype=torch.float16, device="cuda", generator=torch.Generator("cuda").manual_seed(5))
+    y = sbvr.row_deq_mm_T(x, w_t)
+    ref = x.double() @ w_t.decode().double()
+    assert ((y.double() - ref).abs().max() / ref.abs().max()).item() <= 2e-3
+    assert torch.equal(y, sbvr.row_deq_mm_T(x, w_t))
+    check_status()

@@ -134,3 +134,31 @@ def test_popcount_product_oracle_matches_its_definition():
     dense = O.linear_from_dense(O.decode(pl["bvr"], pl["coeff_idx"], pl["coeff"]),
                                 O.decode(pr["bvr"], pr["coeff_idx"], pr["coeff"])).astype(np.float64)
     assert np.abs(y - dense).max() / np.abs(dense).max() < 2e-3
+
+
+def test_transposed_product_oracle_matches_the_kernel_loop():
+    """`linear_t_f64` against a literal loop in the order of the reference kernel for the transposed encoding
+    (sbvr/kernels/sbvr_kernel.cu:138-189): word (n/32, k, s), bit n%32, codebook line idx[n/256, k], dot = sum_s c_s * bit_s,
+    sum += x * dot.  The rounded variant is x @ decode() of the same packed tensors."""
+    N, K, S, M = 256, 24, 3, 2
+    p = O.make_packed(K, N, S, G=256, mode="u8", seed=4)               # packed W^T [K rows, N along the bits]
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal((M, K)).astype(np.float16)
+    bias = rng.standard_normal(N).astype(np.float16)
+    bvr, idx, cache = p["bvr"], p["coeff_idx"], p["coeff"].astype(np.float64)
+    ref = np.zeros((M, N))
+    for m in range(M):
+        for n in range(N):
+            s_ = float(bias[n])
+            for k in range(K):
+                dot = 0.0
+                for s in range(S):
+                    bit = (int(bvr[n // 32, k, s]) >> (n % 32)) & 1
+                    dot += cache[idx[n // 256, k], s] * bit
+                s_ += float(x[m, k]) * dot
+            ref[m, n] = s_
+    y = O.linear_t_f64(x, bvr, idx, p["coeff"], bias)
+    assert np.abs(y - ref).max() <= 1e-12 * max(1.0, np.abs(ref).max())
+    Wt = O.decode(bvr, idx, p["coeff"]).astype(np.float64)
+    yr = O.linear_t_f64(x, bvr, idx, p["coeff"], bias, rounded=True)
+    assert np.allclose(yr, x.astype(np.float64) @ Wt + bias.astype(np.float64)[None, :], rtol=0, atol=1e-12)
