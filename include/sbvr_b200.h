@@ -142,6 +142,20 @@ SBVR_API int sbvr_linear_t_f16(const void* x, const uint32_t* bvr_t, const void*
                                int C, const void* bias, void* y, int M, int N, int K, int S, int G, sbvr_workspace_t* ws,
                                sbvr_stream_t stream);
 
+/* ---- the arithmetic core of the encoder (reference sbvr/core.py:360-722; group length 256) -----------------------
+ * mse[b, c] = mean over the 256 values of group b of min_j fp16((d - point[c, j])^2), point[c, j] = the j-th of the 2^S sums of
+ * line c, every step rounded as the reference's fp16 tensor ops round (`_get_min_mse_coeff` / `_data_diff_min_mse`,
+ * sbvr/core.py:485-500, :520-527).  data fp16 [groups, 256], lines fp16 [L, S], mse fp32 [groups, L]; S in 1..4. */
+SBVR_API int sbvr_encode_mse_f16(const void* data, int groups, const void* lines, int L, int S, float* mse,
+                                 sbvr_stream_t stream);
+/* sel[b, e] = the first j that minimises fp16((data[b, e] - point[which[b], j])^2): the `coeff_comb_sel` of the winning line
+ * (sbvr/core.py:494-498).  which int32 [groups] (device), sel uint8 [groups, 256]. */
+SBVR_API int sbvr_encode_select_f16(const void* data, int groups, const void* lines, const int* which, int S, uint8_t* sel,
+                                    sbvr_stream_t stream);
+/* Selectors uint8 [N, Kp] -> bit-planes uint32 [Kp/32, N, S], plane 0 = most significant selector bit, element 32 kw + i in
+ * bit i (`_change_coeff_sel_to_bvr` and the layout change of `_encode_to_sbvr`, sbvr/core.py:842-876, :783). */
+SBVR_API int sbvr_encode_pack(const uint8_t* sel, int N, int Kp, int S, uint32_t* bvr, sbvr_stream_t stream);
+
 /* ---- the kernels between the linears of a Llama decoder layer ----------------------------------------------
  * Each replaces a chain of eager PyTorch ops of the reference model (models/sbvr_llama.py) by one launch.
  * All tensors fp16, contiguous, 16-byte aligned unless noted. */

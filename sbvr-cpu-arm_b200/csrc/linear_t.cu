@@ -14,7 +14,8 @@
 // word is read once per lane.  Here a THREAD owns one k at a time and all 32 outputs of the word: the lanes of a warp
 // read 32 consecutive k of one word row (S * 128 contiguous bytes, one 16-byte load per lane for S = 4), the codebook
 // index of (group, k) and the activation, and add x * c_s to the accumulators whose bit is set: one predicated add per
-// plane bit, no shifts (with several activation rows the element is dequantised once and costs one FMA per row).  32 fp32 accumulators per activation row live in registers; at the end a butterfly
+// plane bit, no shifts (with several activation rows the element is dequantised once and costs one FMA per row).
+// 32 fp32 accumulators per activation row live in registers; at the end a butterfly
 // reduce-scatter over the lanes (31 shuffles per row, a fixed tree) leaves the sum of output n = lane in each lane, the
 // warps of the block are added in order through shared memory.  A block covers one word row (32 outputs) and a
 // contiguous part of K; when K is split over several blocks (small N), the partial sums go to the workspace and the

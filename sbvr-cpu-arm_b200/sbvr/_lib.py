@@ -47,6 +47,12 @@ lib.sbvr_popc_mm_f16.argtypes = [_vp, _vp, _i, _vp, _i, _i, _vp, _vp, _i, _vp, _
 lib.sbvr_popc_mm_f16.restype = _i
 lib.sbvr_linear_t_f16.argtypes = [_vp, _vp, _vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp]
 lib.sbvr_linear_t_f16.restype = _i
+lib.sbvr_encode_mse_f16.argtypes = [_vp, _i, _vp, _i, _i, _vp, _vp]
+lib.sbvr_encode_mse_f16.restype = _i
+lib.sbvr_encode_select_f16.argtypes = [_vp, _i, _vp, _vp, _i, _vp, _vp]
+lib.sbvr_encode_select_f16.restype = _i
+lib.sbvr_encode_pack.argtypes = [_vp, _i, _i, _i, _vp, _vp]
+lib.sbvr_encode_pack.restype = _i
 lib.sbvr_linear_f16_host.argtypes = [_vp, _vp, _vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp]
 lib.sbvr_linear_f16_host.restype = _i
 lib.sbvr_linear_f16_noalloc.argtypes = [_vp, _vp, _vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp]
@@ -71,7 +77,7 @@ lib.sbvr_argmax_f16.restype = _i
 lib.sbvr_allreduce_add_rmsnorm_f16.argtypes = [_vp, _vp, _vp, _i, _i, _i, _i, _sz, _vp, _vp, _vp, _vp, _i, _i, _f, _vp, _vp]
 lib.sbvr_allreduce_add_rmsnorm_f16.restype = _i
 
-EXPORTS = ["sbvr_popc_mm_f16", "sbvr_linear_t_f16", "sbvr_rope_attention_f16", "sbvr_linear_fused_f16", "sbvr_allreduce_add_rmsnorm_f16", "sbvr_add_rmsnorm_f16", "sbvr_rope_append_f16", "sbvr_attention_f16", "sbvr_silu_mul_f16",
+EXPORTS = ["sbvr_popc_mm_f16", "sbvr_linear_t_f16", "sbvr_encode_mse_f16", "sbvr_encode_select_f16", "sbvr_encode_pack", "sbvr_rope_attention_f16", "sbvr_linear_fused_f16", "sbvr_allreduce_add_rmsnorm_f16", "sbvr_add_rmsnorm_f16", "sbvr_rope_append_f16", "sbvr_attention_f16", "sbvr_silu_mul_f16",
            "sbvr_embedding_f16", "sbvr_argmax_f16", "sbvr_linear_f16_noalloc", "sbvr_workspace_bytes", "sbvr_strerror", "sbvr_last_cuda_error", "sbvr_query", "sbvr_workspace_create",
            "sbvr_workspace_destroy", "sbvr_workspace_status", "sbvr_decode_f16", "sbvr_linear_f16",
            "sbvr_linear_f16_host"]

@@ -140,9 +140,8 @@ class sbvr(torch.nn.Module):
             raise ValueError(_r_str("The ARM CPU tensor layouts (cpu_kernel / cpu_kernel_v2) are not supported: "
                                     "this build runs the GPU layout on B200 only"))
         if data is not None:
-            raise NotImplementedError(
-                "Encoding a dense tensor (the coefficient search of reference sbvr/core.py:360-722) is outside "
-                "this library; encode with the reference and `sbvr.load` the file, or use `sbvr.from_packed`")
+            self._encode(data, encoder_config, device, trans)
+            return
         if not isinstance(sbvr_serialized, _sbvr_serialized):
             raise ValueError(_r_str("Serialized SBVR object is not valid"))
         _device = device if device is not None else torch.device("cuda")
@@ -163,6 +162,26 @@ class sbvr(torch.nn.Module):
                                                                                requires_grad=False)
 
     # -- construction ---------------------------------------------------------------------
+    def _encode(self, data, encoder_config, device, trans):
+        """`sbvr(data, encoder_config)` (reference sbvr/core.py:243-276): encode a dense tensor on the GPU.  `trans=True`
+        encodes the transpose (groups along the other dimension), as there (:244-245)."""
+        from . import encoder
+        if not isinstance(data, torch.Tensor):
+            raise ValueError(_r_str("Data must be a torch tensor"))
+        if trans:
+            data = data.transpose(0, 1).contiguous()
+        conf = encoder.EncoderConfig.from_dict(encoder_config)
+        dev = torch.device(device) if device is not None else torch.device("cuda")
+        self.num_sums, self.bvr_len = conf.num_sums, BVR_LEN
+        self.compute_dtype, self.bvr_dtype = torch.float16, torch.uint32
+        self.original_dtype, self.original_data_shape = data.dtype, data.shape
+        self.input_num_sums, self.input_coeff = -1, None
+        bvr, idx, cache, self.encoder_stats = encoder.encode(data, conf, dev)
+        self._install(bvr, idx, cache, dev)
+        if self.verbose_level > 0:
+            print(f"Encoding complete. {self.encoder_stats}")
+            print(self.get_sbvr_info())
+
     def _install(self, bvr, coeff_idx, coeff_cache, device):
         self.bvr = torch.nn.Parameter(bvr.to(device).contiguous(), requires_grad=False)
         self.coeff_idx = None if coeff_idx is None else torch.nn.Parameter(coeff_idx.to(device).contiguous(),

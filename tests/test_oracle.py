@@ -162,3 +162,22 @@ def test_transposed_product_oracle_matches_the_kernel_loop():
     Wt = O.decode(bvr, idx, p["coeff"]).astype(np.float64)
     yr = O.linear_t_f64(x, bvr, idx, p["coeff"], bias, rounded=True)
     assert np.allclose(yr, x.astype(np.float64) @ Wt + bias.astype(np.float64)[None, :], rtol=0, atol=1e-12)
+
+
+@pytest.mark.parametrize("name", ["enc_s2", "enc_s3"])
+def test_encoder_restatement_reproduces_the_reference_encoder(golden, name):
+    """The sequential encoder walk of oracle/encoder_ref.py, fed with the package's search-space generator (generated on
+    the CPU, as the reference run that made the golden vectors did), gives the reference encoder's codebook, indices and
+    bit-planes bit for bit."""
+    import torch
+    from oracle import encoder_ref as E
+    from sbvr import encoder
+    c = golden[name]
+    S = int(c["S"])
+    W = torch.from_numpy(c["W"])
+    conf = encoder.EncoderConfig(num_sums=S, space_device="cpu")
+    r = E.encode(W, S, lambda g, ext: encoder.group_search_space(g, conf, ext))
+    N, Kp = W.shape[0], r["Kp"]
+    assert np.array_equal(r["lines"].view(np.uint16), c["coeff_cache"].view(np.uint16))
+    assert np.array_equal(r["line_of"].reshape(N, Kp // 256).T, c["coeff_idx"].astype(np.int64))
+    assert np.array_equal(O.pack_bvr(r["sel"].reshape(N, Kp).astype(np.int64), S), c["bvr"])
