@@ -346,8 +346,20 @@ def small_m_and_prefill(torch, dev, stream):
             gbs = alg_bytes(M, N, K) / us / 1e3
             rowdeq.append({"N": N, "K": K, "M": M, "us": round(us, 2), "GBps": round(gbs, 1), "frac": round(gbs / peak, 4)})
         del wt_
+    # the encoder: a 4096 x 4096 weight (randn * 0.02, the reference's recipe) to packed form, wall clock including the host walk
+    import time
+    Wd = (torch.randn((4096, 4096), device=dev, generator=gen) * 0.02).half()
+    sbvr.sbvr(Wd[:64], encoder_config={"num_sums": S}, device=dev, verbose_level=0)      # warm-up
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    we = sbvr.sbvr(Wd, encoder_config={"num_sums": S}, device=dev, verbose_level=0)
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    rel = float(((we.decode().float() - Wd.float()) ** 2).mean() / (Wd.float() ** 2).mean())
+    enc = {"shape": [4096, 4096], "S": S, "seconds": round(dt, 3), "groups_per_s": round(65536 / dt),
+           "relative_mse": round(rel, 5), **we.encoder_stats}
     return {"small_m_sweep": {"S": S, "G": G, "rows": sweep}, "prefill_gemm": prefill,
-            "row_deq_transposed_layout": {"S": S, "G": G, "rows": rowdeq}}
+            "row_deq_transposed_layout": {"S": S, "G": G, "rows": rowdeq}, "encoder": enc}
 
 
 def llama_decode(torch, dev, dist, world, preset, batch, prompt, new_tokens):
@@ -493,6 +505,26 @@ def kernel_case(which):
     dev = torch.device("cuda", 0)
     gen = torch.Generator(device=dev).manual_seed(7)
     N, K = 14336, 4096
+    if which == "rowdeq":
+        # the transposed encoding: packed W^T, i.e. a [K rows, N along the bits] matrix in the same layout
+        wt_ = []
+        for _ in range(6):
+            bvr = torch.randint(-2**31, 2**31 - 1, (N // 32, K, S), dtype=torch.int32, device=dev, generator=gen)
+            idx = torch.randint(0, C, (N // G, K), device=dev, generator=gen).to(torch.int16).view(torch.uint16)
+            cache = (torch.randn((C, S), device=dev, generator=gen) * 0.01).half()
+            wt_.append(sbvr.sbvr.from_packed(bvr, idx, cache, group_len=G, device=dev))
+        x = torch.randn((1, K), device=dev, generator=gen).half()
+        for _ in range(3):
+            for w in wt_:
+                y = sbvr.row_deq_mm_T(x, w)
+        torch.cuda.synchronize()
+        print(json.dumps({"kernel_case": which, "launches": 18, "mean_abs_y": float(y.float().abs().mean())}))
+        return
+    if which == "encode":
+        W = (torch.randn((1024, 4096), device=dev, generator=gen) * 0.02).half()
+        w = sbvr.sbvr(W, encoder_config={"num_sums": S}, device=dev, verbose_level=0)
+        print(json.dumps({"kernel_case": which, **w.encoder_stats}))
+        return
     M = {"gemv": 1, "gemm16": 16, "gemm2048": 2048}[which]
     ws_ = []
     for _ in range(6):
@@ -518,7 +550,7 @@ def main():
     ap.add_argument("--no-extras", action="store_true",
                     help="only the headline GEMV measurement (no M sweep, prefill GEMM or Llama decode sections)")
     ap.add_argument("--skip-70b", action="store_true", help="leave the 70B decode out of the Llama section")
-    ap.add_argument("--kernel-case", default=None, choices=["gemv", "gemm16", "gemm2048", "decode_step"],
+    ap.add_argument("--kernel-case", default=None, choices=["gemv", "gemm16", "gemm2048", "decode_step", "rowdeq", "encode"],
                     help="run a few launches of one kernel on 14336x4096 weights, or one eager decode step of a "
                          "4-layer Llama-3-8B-shaped model inside the NVTX range 'decode', and exit (for profilers)")
     args = ap.parse_args()

@@ -90,3 +90,21 @@ def test_batched_lookup_equals_the_sequential_walk():
     t = sbvr.sbvr(W[:, :256].contiguous(), encoder_config={"num_sums": 2}, verbose_level=0, trans=True)
     assert tuple(t.bvr.shape) == (8, 256, 2)                               # W^T is [256, 48], padded to 256 along the bits
     assert tuple(t.decode().shape) == (256, 48)
+
+
+def test_encode_then_linear_end_to_end():
+    """A really encoded weight (not synthetic planes) through the decode GEMV and the batched GEMM: the product with the
+    packed weight equals x @ decode().T within the fp16 tolerance, and stays close to the product with the dense weight."""
+    import sbvr
+    g = torch.Generator().manual_seed(42)
+    W = (torch.randn((1024, 4096), generator=g) * 0.02).half().cuda()
+    w = sbvr.sbvr(W, encoder_config={"num_sums": 4}, verbose_level=0)
+    Wd = w.decode()
+    assert float(((Wd.float() - W.float()) ** 2).mean() / (W.float() ** 2).mean()) < 0.02
+    for M in (1, 16):
+        x = torch.randn((M, 4096), generator=g).half().cuda()
+        y = sbvr.linear(x, w).double()
+        ref = x.double() @ Wd.double().T
+        assert float((y - ref).abs().max() / ref.abs().max()) <= 1e-2
+        dense = x.double() @ W.double().T
+        assert float((y - dense).abs().max() / dense.abs().max()) < 0.2
