@@ -228,10 +228,11 @@ extern "C" int sbvr_linear_t_f16(const void* x, const uint32_t* bvr_t, const voi
     if (rc) return rc;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     const int nwords = N / 32;
-    // K is split over blocks until about four blocks per SM exist (one resident wave at 64 registers per thread; measured
+    // K is split over blocks while at most four blocks per SM exist (one resident wave at 64 registers per thread; measured
     // best on the Llama-3-8B layer shapes); parts are multiples of the block's 256 k
     const int mt_all = M >= 3 ? 4 : M;            // rows per launch as instantiated: 1, 2 or 4
-    int KS = (4 * di.sm_count + nwords - 1) / nwords;
+    int KS = 4 * di.sm_count / nwords;             // rounded down: all blocks resident at once
+    if (KS < 1) KS = 1;
     int kchunk = ((K + KS - 1) / KS + LT_THREADS - 1) / LT_THREADS * LT_THREADS;
     if (kchunk < 2 * LT_THREADS) kchunk = 2 * LT_THREADS;
     KS = (K + kchunk - 1) / kchunk;
