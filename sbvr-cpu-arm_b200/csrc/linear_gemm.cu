@@ -424,17 +424,25 @@ __global__ void __launch_bounds__(GM_THREADS, 1) linear_gemm_kernel(const GmPara
 
         auto decode_stage = [&](const Pos& q, const uint32_t (&w)[2][S], const unsigned short (&c)[S]) {
             while (ep_item < q.item) epilogue();   // items whose stages have all been handed to the issuer
-            uint32_t hc[S];                        // (c_s / 2, c_s / 2)
-            float sum = 0.0f;
+            // A lone bit at position 10 .. 14 of a half is the number 2^-14, 2^-13, 2^-11, 2^-7, 2^1: masking a packed
+            // word with 0x04000400 << i leaves (bit, bit + 16) as such a half2, and one HFMA2 with c_s divided by that
+            // number adds c_s where the bit is set.  Three shifted copies of the word bring all 16 bit pairs into the
+            // window, so an element pair costs one mask and one HFMA2 per plane (the integer pipe, half as wide as the
+            // fp16 pipe, was this kernel's limit with a shift and a mask-xor per pair).  |c_s| >= 4 would overflow the
+            // largest multiplier: such a row takes the sign-flip form below instead.
+            bool big = false;
+            __half2 mul[S][5];
 #pragma unroll
             for (int s = 0; s < S; ++s) {
-                const float ch = __half2float(__ushort_as_half(c[s])) * 0.5f;
-                sum += ch;
-                const uint32_t hb = (uint32_t)__half_as_ushort(__float2half_rn(ch));
-                hc[s] = hb | (hb << 16);
+                const __half ch = __ushort_as_half(c[s]);
+                big |= !(__habs(ch) < __float2half_rn(3.9f));
+                const __half2 c2 = __half2half2(ch);
+                mul[s][0] = __hmul2(c2, __float2half2_rn(16384.0f));
+                mul[s][1] = __hmul2(c2, __float2half2_rn(8192.0f));
+                mul[s][2] = __hmul2(c2, __float2half2_rn(2048.0f));
+                mul[s][3] = __hmul2(c2, __float2half2_rn(128.0f));
+                mul[s][4] = __hmul2(c2, __float2half2_rn(0.5f));
             }
-            const uint32_t bb = (uint32_t)__half_as_ushort(__float2half_rn(sum));
-            const uint32_t base2 = bb | (bb << 16);
             const int slot = q.it % GM_ASLOTS;
             if (!dead && !mbar_wait_async(&a_empty[slot], ((uint32_t)(q.it / GM_ASLOTS) & 1u) ^ 1u)) {
                 dead = true;
@@ -444,18 +452,52 @@ __global__ void __launch_bounds__(GM_THREADS, 1) linear_gemm_kernel(const GmPara
             if (dead) return;
             gm_fence_after();
             uint32_t a[32];
+            if (!__any_sync(0xffffffffu, big)) {
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
+                for (int h = 0; h < 2; ++h) {
+                    __half2 acc[16];
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    __half2 acc = *reinterpret_cast<const __half2*>(&base2);
+                    for (int j = 0; j < 16; ++j) acc[j] = __float2half2_rn(0.0f);
 #pragma unroll
                     for (int s = 0; s < S; ++s) {
-                        const uint32_t v = w[h][s] << (15 - j);
-                        const uint32_t t = (~v & 0x80008000u) ^ hc[s];
-                        acc = __hadd2(acc, *reinterpret_cast<const __half2*>(&t));
+                        // window copies: bits 0..4 / 5..9 / 10..14 / 15 of each half at positions 10..14 / 10..14 / 10..14 / 14
+                        const uint32_t v0 = w[h][s] << 10, v1 = w[h][s] << 5, v2 = w[h][s], v3 = w[h][s] >> 1;
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const uint32_t v = (j < 5) ? v0 : (j < 10) ? v1 : (j < 15) ? v2 : v3;
+                            const int pos = (j < 15) ? j % 5 : 4;
+                            const uint32_t t = v & (0x04000400u << pos);
+                            acc[j] = __hfma2(*reinterpret_cast<const __half2*>(&t), mul[s][pos], acc[j]);
+                        }
                     }
-                    a[16 * h + j] = *reinterpret_cast<const uint32_t*>(&acc);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) a[16 * h + j] = *reinterpret_cast<const uint32_t*>(&acc[j]);
+                }
+            } else {
+                uint32_t hc[S];                    // (c_s / 2, c_s / 2)
+                float sum = 0.0f;
+#pragma unroll
+                for (int s = 0; s < S; ++s) {
+                    const float chf = __half2float(__ushort_as_half(c[s])) * 0.5f;
+                    sum += chf;
+                    const uint32_t hb = (uint32_t)__half_as_ushort(__float2half_rn(chf));
+                    hc[s] = hb | (hb << 16);
+                }
+                const uint32_t bb = (uint32_t)__half_as_ushort(__float2half_rn(sum));
+                const uint32_t base2 = bb | (bb << 16);
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        __half2 acc = *reinterpret_cast<const __half2*>(&base2);
+#pragma unroll
+                        for (int s = 0; s < S; ++s) {
+                            const uint32_t v = w[h][s] << (15 - j);
+                            const uint32_t t = (~v & 0x80008000u) ^ hc[s];
+                            acc = __hadd2(acc, *reinterpret_cast<const __half2*>(&t));
+                        }
+                        a[16 * h + j] = *reinterpret_cast<const uint32_t*>(&acc);
+                    }
                 }
             }
             gm_st32(tbase + lane_sel + GM_A_COL + slot * 32, a);
