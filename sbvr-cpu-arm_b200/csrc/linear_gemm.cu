@@ -7,12 +7,13 @@
 //
 //  A (weights, from tensor memory)  Decoder thread r of a warpgroup owns weight row r of the tile.  Per 64 k it
 //      loads its 2 x S packed words, turns them into 64 fp16 values and stores them to its tensor-memory lane
-//      (tcgen05.st): decoded weights never touch shared or global memory.  The value of an element is
-//          base + sum_s (+-)(c_s / 2),   base = sum_s c_s / 2,  sign + where the plane bit is 1,
-//      formed two elements at a time: `w << (15 - j)` moves bits j and j + 16 of a packed word to the sign
-//      positions of a half2, one LOP3 turns that into (+-c_s/2, +-c_s/2), one HADD2 accumulates: three
-//      instructions per plane per pair of elements.  Elements j and j + 16 of a word share a 32-bit column, so
-//      the K order inside each 32-k word is permuted (position p <-> k = p/2 + 16 (p & 1)).
+//      (tcgen05.st): decoded weights never touch shared or global memory.  The value of an element is the sum of
+//      the c_s whose plane bit is set, formed two elements at a time in half2: a lone bit at position 10 .. 14 of a
+//      half is a power of two, so `word & (0x04000400 << i)` is (2^e * bit_j, 2^e * bit_{j+16}) and one HFMA2 with
+//      c_s / 2^e adds c_s where the bits are set: a mask and an HFMA2 per plane per pair of elements, plus three
+//      shifted copies per word (rows with |c_s| >= 3.9 use sign flips around sum_s c_s / 2 instead: shift, LOP3,
+//      HADD2).  Elements j and j + 16 of a word share a 32-bit column, so the K order inside each 32-k word is
+//      permuted (position p <-> k = p/2 + 16 (p & 1)).
 //  B (activations, from shared memory)  x is first re-tiled by a small kernel into the blocked layout the MMA
 //      reads (8-row x 16-byte core matrices, K-major, no swizzle) with the same K permutation, one contiguous
 //      block per (NX rows, 64 k); the GEMM fetches a block with a single bulk asynchronous copy.
