@@ -117,3 +117,26 @@ def test_glue_and_fused_entry_points_validate_before_any_cuda_call():
     assert L.sbvr_allreduce_add_rmsnorm_f16(p, p, p, 3, 0, 0, 2, 4096, p, p, p, p, 1, 4096, 1e-5, None, None) == -1
     out = ctypes.c_size_t(0)
     assert L.sbvr_workspace_bytes(0, 0, 64, 256, ctypes.byref(out)) == -1
+
+
+def test_encoder_config_and_search_space_on_cpu():
+    """Host side of the encoder: unknown keys are ignored, unsupported settings are refused, and the candidate lines of a
+    group have the reference's counts (r x b x s lists plus the plain grid; sbvr/core.py:400-483) and are sorted by
+    magnitude inside each line."""
+    import pytest
+    import torch
+    from sbvr import encoder
+    conf = encoder.EncoderConfig.from_dict({"num_sums": 3, "verbose": 1})
+    assert conf.num_sums == 3 and conf.r_search_num == 64
+    with pytest.raises(ValueError):
+        encoder.EncoderConfig.from_dict({"num_sums": 5})
+    with pytest.raises(ValueError):
+        encoder.EncoderConfig.from_dict({"error_function": "input_inner"})
+    g = torch.Generator().manual_seed(0)
+    d = (torch.randn(256, generator=g) * 0.02).half()
+    space = encoder.group_search_space(d, encoder.EncoderConfig(num_sums=4, space_device="cpu"), False)
+    assert space.dtype == torch.float16 and space.shape == (64 * 40 * 40 + 20 ** 4, 4)
+    a = space.abs().float()
+    assert bool((a[:, 1:] >= a[:, :-1]).all())
+    with pytest.raises(RuntimeError):
+        encoder.encode(d.view(1, -1), encoder.EncoderConfig(), device=torch.device("cpu"))
