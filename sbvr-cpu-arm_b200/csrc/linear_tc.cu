@@ -30,14 +30,14 @@
 // Replaces cuda_1xtN_rd_WP8_TBW4_NS4 / cuda_row_deq_mm_T (reference sbvr/kernels/sbvr_kernel.cu:284-359,
 // :121-191), whose per-bit select + FMA needs 3-5x more issue slots than HBM3e leaves per element.
 //
-// Structure: one CTA per SM, 19 warps.  A CTA owns whole row tiles (128 MMA rows = 32 output rows
+// Structure: one CTA per SM, 21 warps.  A CTA owns whole row tiles (128 MMA rows = 32 output rows
 // for S = 3, 4; 64 for S = 2) and takes them round-robin; inside a row tile the four compute
 // warpgroups split K into four contiguous quarters, so no partial sum ever leaves the SM.
-// Thread r of a warpgroup owns MMA row r: it loads the 8 packed words of its row per 256 k straight
-// from global memory (a warp reads 128 contiguous bytes per word row; loads run three tiles ahead
-// of their use), expands them and stores them to its tensor-memory lane, then signals an
-// mbarrier.  Two issuer warps (each serving two warpgroups) wait on those barriers and issue the
-// four K = 64 MMAs of a tile from one elected lane of a converged warp (a lone divergent thread
+// Thread r of a warpgroup owns MMA row r: the 8 packed words of its row per 256 k come from global
+// memory through a per-warp cp.async ring in shared memory (a warp reads 128 contiguous bytes per
+// word row; loads run three tiles ahead of their use); it expands them, stores them to its
+// tensor-memory lane and signals an mbarrier.  Four issuer warps (one per warpgroup) wait on those
+// barriers and issue the four K = 64 MMAs of a tile from one elected lane of a converged warp (a lone divergent thread
 // needs about twice as long per tcgen05.mma).  A and D are double buffered in tensor memory so that
 // the MMAs of a tile overlap the expansion of the next and the epilogue of the previous one.
 // When a warpgroup has finished its quarter of a row tile it leaves its fp32 sums in shared memory;
