@@ -61,7 +61,9 @@ SBVR_API int sbvr_last_cuda_error(void);
  * bound at :153), which cached cudaDeviceProp for every device and printed them.  Any out pointer may be NULL. */
 SBVR_API int sbvr_query(int device, int* sm_count, int* smem_per_block_optin, int* l2_bytes, int* cc_major, int* cc_minor);
 
-/* Scratch memory: the device status word of the bounded waits, staging buffers of the host-pointer entry point.
+/* Scratch memory: the device status word of the bounded waits, the quantised activations and the partial sums of
+ * row tiles shared by two CTAs (decode kernel), the re-tiled activations and split-K partial sums (batched kernel),
+ * staging buffers of the host-pointer entry point.
  * The reference allocates nothing comparable (its kernels keep everything in registers); it does allocate
  * the output inside the binding (sbvr/kernels/sbvr_ops.cpp:100-101), which here is the caller's job.
  * `bytes` = 0 picks a default that covers every Llama-3 8B/70B layer shape up to 32 activation rows.
@@ -90,8 +92,10 @@ SBVR_API int sbvr_decode_f16(const uint32_t* bvr, const void* coeff_idx, int idx
  * Llama flow runs (sbvr_utils/utils_llama.py:147, test_sbvr.py:321).  K must be the padded length
  * (multiple of G).  `ws` may be NULL only for the kernels that need no scratch (see `algo`).
  *   algo 0 = pick; 1 = SIMT dequantise-and-FMA kernel (any S <= 8, no workspace);
- *   2 = tcgen05 FP4 tensor-core kernel for decode (S in {2,3,4}, M <= 4, N a multiple of 32 (64 for S = 2),
- *       K a multiple of 256; needs a workspace for its status word);
+ *   2 = tcgen05 FP4 tensor-core kernel for decode (S in {2,3,4}, G in {128,256}, M <= 4, N a multiple of 32 (64 for
+ *       S = 2) and at most 262144, K a multiple of 256, M * K <= about 90 K elements (the activation digits stay in shared
+ *       memory), bvr / coeff_idx / coeff / x 16-byte aligned; needs a workspace: status word, activation digits,
+ *       partial sums);
  *   3 = tcgen05 fp16 GEMM with in-kernel dequantisation for batches and prefill (S in {2,3,4}, any M,
  *       N a multiple of 128; needs a workspace of sbvr_workspace_bytes(...)). */
 SBVR_API int sbvr_linear_f16(const void* x, const uint32_t* bvr, const void* coeff_idx, int idx_bytes, const void* coeff,
@@ -111,10 +115,14 @@ SBVR_API int sbvr_linear_f16_host(const void* x_host, const uint32_t* bvr, const
  * workspace: the kernels' scratch is a fixed 4 MiB array inside the library's device image (held by every GPU that
  * loads the library, until exit), and neither this call nor anything under it allocates or frees.
  *   - Calls on one device share that array: calls that can overlap on the GPU race; serialise them.
- *   - The first call on a device resolves the array's address and sets kernel attributes: make it outside stream
- *     capture, with that device current.
- *   - Problems whose scratch exceeds the array return SBVR_ERR_NOALLOC_LIMIT and launch nothing (all Llama-3
- *     8B/70B layer shapes at M <= 4 fit).
+ *   - The first call of each kernel variant (S, G, M, index width) on a device resolves the array's address, sets
+ *     kernel attributes and may encode a tensor map: make such first calls outside stream capture, with that device
+ *     current.
+ *   - M <= 4 runs on the decode kernel (about 4 K M bytes of activation digits + 150 KB of partial sums: always
+ *     fits); larger M runs on the batched tensor-core kernel, whose re-tiled activations (about 2 M K bytes) and
+ *     split-K partial sums must fit the array: M = 128 at K = 14336 fits, M = 2048 does not.  A problem that does not
+ *     fit returns SBVR_ERR_NOALLOC_LIMIT and launches nothing.  Shapes neither kernel covers run on the SIMT kernel,
+ *     which needs no scratch.
  * It has no counterpart in the reference, whose bindings allocate their output on every call
  * (sbvr/kernels/sbvr_ops.cpp:100-101). */
 SBVR_API int sbvr_linear_f16_noalloc(const void* x, const uint32_t* bvr, const void* coeff_idx, int idx_bytes,
@@ -204,14 +212,15 @@ SBVR_API int sbvr_embedding_f16(const int* ids, const void* table, void* out, in
 SBVR_API int sbvr_argmax_f16(const void* logits, int* out, float* scratch, int rows, int vocab, sbvr_stream_t stream);
 
 /* ---- decode linears with the preceding element-wise op folded in ---------------------------------------------
- * The decode GEMV (algo 2 of sbvr_linear_f16: M <= 4, N % 32 == 0, K % 256 == 0) brings the whole activation row
- * into every CTA anyway, so the op in front of the linear can be applied on the way in instead of in a launch of
- * its own:
+ * The decode GEMV (algo 2 of sbvr_linear_f16: M <= 4, N % 32 == 0, K % 256 == 0) turns the activation row into
+ * block-fixed-point digits in a small kernel of its own before the product; the op in front of the linear is applied
+ * there instead of in a launch of its own:
  *   SBVR_XOP_SILU_MUL     x = fp16(silu(g)) * u, `x` pointing at rows [g (K) | u (K)] of pitch 2K
  *                         (LlamaMLP.forward, models/sbvr_llama.py:238-240, in front of down_proj)
  *   SBVR_XOP_ADD_RMSNORM  x = norm_weight * fp16((h + delta) * rsqrt(mean((h + delta)^2) + eps)) with h = `x`
  *                         (pitch K), delta NULL = no add; h + delta is also stored to h_out (may be NULL; must be a
- *                         buffer other than h) (LlamaDecoderLayer.forward :395-406 + LlamaRMSNorm.forward :118-123)
+ *                         buffer other than h and delta: both are still being read while it is written; overlap is
+ *                         refused with SBVR_ERR_BAD_ARG) (LlamaDecoderLayer.forward :395-406 + LlamaRMSNorm.forward :118-123)
  * Same rounding as sbvr_silu_mul_f16 / sbvr_add_rmsnorm_f16 followed by sbvr_linear_f16.  Returns
  * SBVR_ERR_UNSUPPORTED where the decode GEMV does not apply (the caller then runs the separate kernels). */
 enum { SBVR_XOP_NONE = 0, SBVR_XOP_SILU_MUL = 1, SBVR_XOP_ADD_RMSNORM = 2 };

@@ -1,5 +1,5 @@
 // C ABI of sbvr_b200: argument validation, workspace management and dispatch.  Nothing here
-// computes; see decode.cu, linear_simt.cu, linear_tc.cu.
+// computes; see decode.cu, linear_simt.cu, linear_tcs.cu, linear_gemm.cu.
 #include <cstdlib>
 #include <mutex>
 
@@ -120,8 +120,8 @@ int sbvr_workspace_create(sbvr_workspace_t** out, int device, size_t bytes) {
     ws->counters = reinterpret_cast<unsigned int*>(ws->base + 256);
     ws->dyn = ws->base + fixed;
     ws->dyn_bytes = bytes - fixed;
+    *out = ws;                                     // the workspace exists whatever happens to the device switch below
     SBVR_CUDA_TRY(cudaSetDevice(prev));
-    *out = ws;
     return SBVR_OK;
 }
 
@@ -194,12 +194,16 @@ int sbvr_linear_f16(const void* x, const uint32_t* bvr, const void* coeff_idx, i
         DeviceInfo di;
         algo = 1;
         if (ws && device_info(ws->device, &di) == SBVR_OK && di.cc_major == 10) {
-            if (linear_tc_supported(w, M) && !(reinterpret_cast<uintptr_t>(x) & 15)) algo = 2;
+            if (linear_tcs_supported(w, M) && !(reinterpret_cast<uintptr_t>(x) & 15) &&
+                linear_tcs_workspace_bytes(w, M, di.sm_count) <= ws->dyn_bytes) algo = 2;
             else if (linear_gemm_supported(w, M) &&
                      linear_gemm_workspace_bytes(w, M, di.sm_count) <= ws->dyn_bytes) algo = 3;
         }
     }
-    if (algo == 2) return launch_linear_tc(xh, w, bh, yh, M, ws, st);
+    if (algo == 2) {
+        if (!ws) return SBVR_ERR_WORKSPACE;
+        return launch_linear_tcs(xh, w, bh, yh, M, ws->device, ws->status, ws->counters, ws->dyn, ws->dyn_bytes, st);
+    }
     if (algo == 3) return launch_linear_gemm(xh, w, bh, yh, M, ws, st);
     return launch_linear_simt(xh, w, bh, yh, M, st);
 }
@@ -218,13 +222,16 @@ int sbvr_linear_fused_f16(int x_op, const void* x, const void* delta, const void
     if (!ws) return SBVR_ERR_WORKSPACE;
     rc = device_info(ws->device, &di);
     if (rc) return rc;
-    if (di.cc_major != 10 || !linear_tc_supported(w, M)) return SBVR_ERR_UNSUPPORTED;
+    if (di.cc_major != 10) return SBVR_ERR_UNSUPPORTED;
     XOp xop;
     xop.op = x_op;
     xop.delta = reinterpret_cast<const __half*>(delta), xop.norm_w = reinterpret_cast<const __half*>(norm_weight);
     xop.h_out = reinterpret_cast<__half*>(h_out), xop.eps = eps;
-    return launch_linear_tc(reinterpret_cast<const __half*>(x), w, reinterpret_cast<const __half*>(bias),
-                            reinterpret_cast<__half*>(y), M, ws, reinterpret_cast<cudaStream_t>(stream), &xop);
+    if (!linear_tcs_supported(w, M)) return SBVR_ERR_UNSUPPORTED;
+    if (linear_tcs_workspace_bytes(w, M, di.sm_count) > ws->dyn_bytes) return SBVR_ERR_WORKSPACE;
+    return launch_linear_tcs(reinterpret_cast<const __half*>(x), w, reinterpret_cast<const __half*>(bias),
+                             reinterpret_cast<__half*>(y), M, ws->device, ws->status, ws->counters, ws->dyn,
+                             ws->dyn_bytes, reinterpret_cast<cudaStream_t>(stream), &xop);
 }
 
 int sbvr_linear_f16_host(const void* x_host, const uint32_t* bvr, const void* coeff_idx, int idx_bytes,

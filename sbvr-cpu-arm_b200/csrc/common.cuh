@@ -7,6 +7,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
+
 #include "../../include/sbvr_b200.h"
 
 namespace sbvr {
@@ -78,9 +80,27 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per device for one kernel instantiation: the caller keeps one
+// static SmemOnce per instantiation.  Safe from several host threads and with several devices in turn.
+struct SmemOnce {
+    std::mutex mu;
+    bool done[64] = {false};
+};
+template <typename Kernel>
+inline int set_max_smem_once(SmemOnce& once, Kernel kernel, int bytes) {
+    int dev = 0;
+    SBVR_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return SBVR_ERR_BAD_ARG;
+    std::lock_guard<std::mutex> lock(once.mu);
+    if (!once.done[dev]) {
+        SBVR_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+        once.done[dev] = true;
+    }
+    return SBVR_OK;
+}
+
 int launch_decode(const PackedW& w, __half* W, int ldw, int Kout, cudaStream_t st);
 int launch_linear_simt(const __half* x, const PackedW& w, const __half* bias, __half* y, int M, cudaStream_t st);
-bool linear_tc_supported(const PackedW& w, int M);
 // What the decode GEMV makes its activations of while it brings them in.
 struct XOp {
     int op;                  // SBVR_XOP_*
@@ -89,8 +109,13 @@ struct XOp {
     __half* h_out;           // ADD_RMSNORM: x + delta is stored here (may be NULL; must not be x)
     float eps;
 };
-int launch_linear_tc(const __half* x, const PackedW& w, const __half* bias, __half* y, int M,
-                     sbvr_workspace* ws, cudaStream_t st, const XOp* xop = nullptr);
+// The decode GEMV (linear_tcs.cu): FP4 tensor-core dot products, weights through TMA, work split by 256-k steps.  The caller hands it its scratch: a status word pair, one zeroed arrival counter per row
+// tile (SBVR_WS_COUNTERS at most) and `scratch_bytes` >= linear_tcs_workspace_bytes() of 256-byte aligned memory.
+bool linear_tcs_supported(const PackedW& w, int M);
+size_t linear_tcs_workspace_bytes(const PackedW& w, int M, int sm_count);
+int launch_linear_tcs(const __half* x, const PackedW& w, const __half* bias, __half* y, int M, int device,
+                      unsigned int* status, unsigned int* counters, char* scratch, size_t scratch_bytes, cudaStream_t st,
+                      const XOp* xop = nullptr);
 bool linear_gemm_supported(const PackedW& w, int M);
 size_t linear_gemm_workspace_bytes(const PackedW& w, int M, int sm_count);
 int launch_linear_gemm(const __half* x, const PackedW& w, const __half* bias, __half* y, int M,

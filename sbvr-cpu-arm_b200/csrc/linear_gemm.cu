@@ -600,14 +600,9 @@ size_t linear_gemm_workspace_bytes(const PackedW& w, int M, int sm_count) {
 
 template <int S, int NX>
 static int gm_launch_inst(const GmParams& p, int grid, int smem, cudaStream_t st) {
-    static int configured_for = -1;
-    int dev = 0;
-    SBVR_CUDA_TRY(cudaGetDevice(&dev));
-    if (configured_for != dev) {
-        SBVR_CUDA_TRY(cudaFuncSetAttribute(linear_gemm_kernel<S, NX>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           227 * 1024));
-        configured_for = dev;
-    }
+    static SmemOnce once;
+    const int rc = set_max_smem_once(once, linear_gemm_kernel<S, NX>, 227 * 1024);
+    if (rc) return rc;
     SBVR_CUDA_TRY(launch_pdl(linear_gemm_kernel<S, NX>, dim3(grid), dim3(GM_THREADS), (size_t)smem, st, p));
     return SBVR_OK;
 }

@@ -1,0 +1,1046 @@
+// Decode-time SBVR linear (M <= 4 activation rows): streamed weights, FP4 tensor-core dot products, balanced split.
+//
+//   y[n] = sum_g sum_s c[g,n,s] * ( sum_{k in g} x[k] * bit_s[n,k] )
+//
+// Arithmetic (shared with the older one-kernel form): the inner sum is a tcgen05.mma kind::mxf4 product of
+//   A  one MMA row per (output row n, plane s); a packed word w becomes four words of eight E2M1 elements
+//      (`w & 0x1111..`, `w & 0x2222..`, `w & 0x4444..`, `(w >> 1) & 0x4444..`: plane bits as {0, 0.5 | 1 | 2 | 2}),
+//      written from registers straight into tensor memory (tcgen05.st), and
+//   B  the activations as eight radix-4 E2M1 digits of a 16-bit block-fixed-point value per group (xdigits.cuh),
+// accumulated exactly in fp32 in tensor memory; per 256 k the epilogue reads the 128 x 8 sums, forms
+// sum_d 4^d D[d], multiplies by the row's fp16 coefficient and the group's step, and accumulates in fp32.
+//
+// What is different here, and why:
+//   * The digits are produced ONCE per call by a small kernel (xquant_kernel, which also applies the op in front of
+//     the linear: nothing, SiLU(gate) * up, or residual add + RMSNorm) and copied into every CTA with one bulk copy,
+//     instead of every CTA spending ~2 500 cycles of its integer pipe on the same activations.
+//   * Weights reach shared memory through TMA tensor copies (one 8 x TN*S-word box per 256-k step and warpgroup,
+//     issued by that warpgroup's issuer warp as soon as the stage is free), not through per-thread cp.async.
+//   * The hand-over compute warps -> issuer is a named hardware barrier (bar.arrive / bar.sync), not an mbarrier poll.
+//   * Work is split by 256-k STEPS, not by row tiles: CTA c owns steps [c T / G, (c + 1) T / G) of the (row tile, k
+//     block) list, so every SM streams the same number of bytes whatever N / 32 mod #SM is.  A CTA's warpgroups take its
+//     steps round-robin.  Per row tile the warpgroups' sums meet in shared memory; a row tile that straddles CTAs is
+//     finished by the last CTA to arrive (partials in scratch, one counter per row tile, summed in CTA order, so the
+//     result is the same bits on every run).  Straddling tiles are processed first, so their exchange is over long
+//     before the CTA ends.
+//   * Every wait is bounded; after a time-out a thread keeps the barrier protocol going but skips the work.
+//
+// Replaces cuda_1xtN_rd_WP8_TBW4_NS4 / cuda_row_deq_mm_T (reference sbvr/kernels/sbvr_kernel.cu:284-359, :121-191).
+#include <cuda.h>
+
+#include <mutex>
+
+#include "common.cuh"
+#include "xdigits.cuh"
+
+namespace sbvr {
+
+constexpr int TS_HDR = 1024;                    // barriers, flags, tensor-memory base
+constexpr int TS_TMEM_COLS = 512;
+constexpr int TS_SF_COL = 480;                  // 32 columns of unit scale factors
+constexpr int TS_MAX_STAGES = 8;
+constexpr int TS_STAGE_WORDS = 4096;            // bytes of packed words per stage
+constexpr int TS_STAGE_BYTES = 4096 + 512;      // + coefficient indices / direct coefficients of the step
+constexpr int TS_BSLACK = 4096;                 // MMA columns beyond M read (and ignore) what follows the digits
+
+__host__ __device__ constexpr int ts_sp(int S) { return S == 2 ? 2 : 4; }            // MMA rows per output row
+__host__ __device__ constexpr int ts_tn(int S) { return 128 / ts_sp(S); }            // output rows per tile
+__host__ __device__ constexpr int ts_mpad(int M) { return M <= 2 ? 2 : 4; }
+__host__ __device__ constexpr int ts_dcols(int NSUB, int M) { return NSUB * 8 * ts_mpad(M); }
+__host__ __device__ constexpr int ts_wgcols(int NSUB, int M) { return 64 + 2 * ts_dcols(NSUB, M); }
+__host__ __device__ constexpr int ts_nwg(int NSUB, int M) {
+    return (TS_SF_COL / ts_wgcols(NSUB, M)) > 5 ? 5 : (TS_SF_COL / ts_wgcols(NSUB, M));
+}
+// Warp roles: warps 0 .. NWG-1 issue (MMAs and copies), warp NWG finishes, compute warps start at the next multiple of
+// four (a warp reaches the tensor-memory lanes 32 (warp % 4) ...).  The issuers have the lowest warp numbers on purpose:
+// the schedulers favour older warps, and an issuer behind twenty ALU-bound compute warps waited 700-1000 cycles for
+// its first issue slot after every hand-over.
+__host__ __device__ constexpr int ts_cw0(int NSUB, int M) { return (ts_nwg(NSUB, M) + 1 + 3) / 4 * 4; }
+__host__ __device__ constexpr int ts_threads(int NSUB, int M) { return (ts_cw0(NSUB, M) + 4 * ts_nwg(NSUB, M)) * 32; }
+__host__ __device__ inline int ts_round_up(int v, int a) { return (v + a - 1) / a * a; }
+
+struct TsParams {
+    const __half* x;              // activations [M][K] when the CTAs quantise them themselves (x_in_kernel), else unused
+    int x_in_kernel;
+    const unsigned char* xq;      // digits [KB][M][1024] then steps float [M][KB * NSUB] (written by xquant_kernel)
+    const void* idx;
+    const __half* coeff;
+    const __half* bias;
+    __half* y;
+    unsigned int* status;
+    float* partials;              // [grid][2][M * TN]
+    unsigned int* counters;       // [NT], zero between calls
+    int N, K, KB, NT, C, cache_in_smem, stages;
+    int xq_bytes;                 // bytes of the digits + steps, a multiple of 16
+    int off_red, off_cache, off_ring, off_b;      // shared-memory carve-up
+};
+
+struct XqParams {
+    const __half* x;
+    unsigned char* xq;
+    int K, KB, M;
+    int x_op;
+    const __half* delta;
+    const __half* norm_w;
+    __half* h_out;
+    float eps;
+};
+
+// ---------------------------------------------------------------------------------------------
+// tcgen05 / TMA wrappers
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void ts_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void ts_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ uint64_t ts_bdesc(uint32_t saddr) {
+    // K-major, no swizzle: core matrices of 8 rows x 16 B; 128 B between the two K chunks of one MMA,
+    // 1024 B between groups of 8 rows; descriptor version 1 (sm_100)
+    return (uint64_t)((saddr & 0x3FFFF) >> 4) | ((uint64_t)(128 >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46);
+}
+
+__device__ __forceinline__ void ts_mma(uint32_t d_t, uint32_t a_t, uint64_t bdesc, uint32_t idesc, uint32_t sfa,
+                                       uint32_t sfb, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.scale_vec::2X [%0], [%1], %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(d_t), "r"(a_t), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+        : "memory");
+}
+
+__device__ __forceinline__ void ts_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+
+__device__ __forceinline__ void ts_st32(uint32_t taddr, const uint32_t (&a)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};" ::"r"(taddr),
+        "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(a[4]), "r"(a[5]), "r"(a[6]), "r"(a[7]), "r"(a[8]), "r"(a[9]),
+        "r"(a[10]), "r"(a[11]), "r"(a[12]), "r"(a[13]), "r"(a[14]), "r"(a[15]), "r"(a[16]), "r"(a[17]), "r"(a[18]),
+        "r"(a[19]), "r"(a[20]), "r"(a[21]), "r"(a[22]), "r"(a[23]), "r"(a[24]), "r"(a[25]), "r"(a[26]), "r"(a[27]),
+        "r"(a[28]), "r"(a[29]), "r"(a[30]), "r"(a[31])
+        : "memory");
+}
+__device__ __forceinline__ void ts_st8(uint32_t taddr, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t a4, uint32_t a5,
+                                       uint32_t a6, uint32_t a7) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(a0), "r"(a1), "r"(a2),
+                 "r"(a3), "r"(a4), "r"(a5), "r"(a6), "r"(a7)
+                 : "memory");
+}
+__device__ __forceinline__ void ts_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// Waits for this thread's tensor-memory loads; the registers are operands so that nothing uses them earlier.
+__device__ __forceinline__ void ts_wait_ld(uint32_t (&r)[8]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7])
+                 :
+                 : "memory");
+}
+
+// Eight columns of this thread's tensor-memory lane; the values are valid after ts_wait_ld().
+__device__ __forceinline__ void ts_ld8_issue(uint32_t taddr, uint32_t (&r)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr)
+                 : "memory");
+}
+
+// One box of a 2-D tensor map, global -> shared, completion counted on an mbarrier.  No multicast.
+__device__ __forceinline__ void ts_tma_2d(void* dst_smem, const CUtensorMap* tmap, int c0, int c1, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(dst_smem)), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(c0), "r"(c1), "r"(smem_u32(bar))
+        : "memory");
+}
+
+__device__ __forceinline__ void ts_bar_arrive(int id, int nthreads) {
+    asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+// ---------------------------------------------------------------------------------------------
+// The list of 256-k steps of a CTA, in the order it processes them.
+//
+// Steps are numbered tile * KB + kb.  CTA c owns [b0, b1).  The row tiles it touches are `nseg` segments; the first
+// and the last may be shared with neighbouring CTAs (they do not cover the whole tile).  Shared segments come first.
+// ---------------------------------------------------------------------------------------------
+struct TsSegs {
+    int b0, b1, KB;
+    int tile_first, tile_last, nseg;
+    int H, L;                     // head / tail shared (only meaningful when nseg > 1; for nseg == 1, H = shared)
+    // T * G < 2^32 is checked by the host (linear_tcs_supported)
+    __host__ __device__ void init(unsigned int T, unsigned int G, unsigned int c, int KB_) {
+        KB = KB_;
+        b0 = (int)(c * T / G);
+        b1 = (int)((c + 1u) * T / G);
+        tile_first = b0 / KB;
+        tile_last = (b1 - 1) / KB;
+        nseg = (b1 > b0) ? tile_last - tile_first + 1 : 0;
+        H = (b0 % KB) != 0;
+        L = (b1 % KB) != 0;
+        if (nseg == 1) H = L = (b1 - b0 < KB);
+    }
+    __host__ __device__ int tile(int q) const {
+        if (nseg <= 1 || !L) return tile_first + q;
+        if (q == H) return tile_last;
+        return q < H ? tile_first : tile_first + q - 1;
+    }
+    __host__ __device__ int k0(int q) const {
+        const int t = tile(q);
+        return (t == tile_first) ? b0 - t * KB : 0;
+    }
+    __host__ __device__ int k1(int q) const {
+        const int t = tile(q);
+        return (t == tile_last) ? b1 - t * KB : KB;
+    }
+    __host__ __device__ bool shared(int q) const { return k1(q) - k0(q) < KB; }
+};
+
+// Position in that list, advanced by a fixed stride (the number of warpgroups).
+struct TsCursor {
+    int q, k, k_end;              // segment, k block inside its tile, end of the segment's k range
+    __device__ void start(const TsSegs& sg, int pos) {
+        q = 0;
+        k = 0, k_end = 0;
+        if (sg.nseg > 0) {
+            k = sg.k0(0) + pos;
+            k_end = sg.k1(0);
+            norm(sg);
+        }
+    }
+    __device__ void norm(const TsSegs& sg) {
+        while (q < sg.nseg && k >= k_end) {
+            const int over = k - k_end;
+            ++q;
+            if (q < sg.nseg) {
+                k = sg.k0(q) + over;
+                k_end = sg.k1(q);
+            }
+        }
+    }
+    __device__ void advance(const TsSegs& sg, int n) {
+        k += n;
+        norm(sg);
+    }
+    __device__ bool done(const TsSegs& sg) const { return q >= sg.nseg; }
+};
+
+// ---------------------------------------------------------------------------------------------
+// activations -> digits, once per call
+// ---------------------------------------------------------------------------------------------
+template <int NSUB>
+__global__ void __launch_bounds__(512) xquant_kernel(const XqParams p) {
+    __shared__ __align__(16) unsigned char area[16][1024];
+    __shared__ float ssum[16];
+    pdl_launch_dependents();
+    pdl_wait();                                    // the activations come from the previous kernel of the stream
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m = blockIdx.y;
+    const int kb = blockIdx.x * 16 + warp;
+    const int K = p.K;
+    float rs = 0.0f;
+    if (p.x_op == SBVR_XOP_ADD_RMSNORM) {
+        // mean of (h + delta)^2 over the whole row, the sum formed in fp16 like the separate kernel does
+        float sq = 0.0f;
+        for (int c = threadIdx.x; c < K / 8; c += 512) {
+            uint4 a = __ldg(reinterpret_cast<const uint4*>(p.x + (size_t)m * K) + c);
+            __half2* ah = reinterpret_cast<__half2*>(&a);
+            if (p.delta) {
+                const uint4 b = __ldg(reinterpret_cast<const uint4*>(p.delta + (size_t)m * K) + c);
+                const __half2* bh = reinterpret_cast<const __half2*>(&b);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) ah[e] = __hadd2(ah[e], bh[e]);
+            }
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 f = __half22float2(ah[e]);
+                sq += f.x * f.x + f.y * f.y;
+            }
+        }
+#pragma unroll
+        for (int o = 16; o; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+        if (lane == 0) ssum[warp] = sq;
+        __syncthreads();
+        float tot = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 16; ++w) tot += ssum[w];
+        rs = rsqrtf(tot / (float)K + p.eps);
+    }
+    if (kb >= p.KB) return;
+    // this warp's 256 activations: lane l brings elements 8 l .. 8 l + 7
+    const size_t off = (size_t)m * K + (size_t)kb * 256 + lane * 8;
+    uint4 o;
+    __half2* oh = reinterpret_cast<__half2*>(&o);
+    if (p.x_op == SBVR_XOP_SILU_MUL) {
+        const __half* gp = p.x + (size_t)m * 2 * K + (size_t)kb * 256 + lane * 8;
+        const uint4 g = __ldg(reinterpret_cast<const uint4*>(gp));
+        const uint4 u = __ldg(reinterpret_cast<const uint4*>(gp + K));
+        const __half2* gh = reinterpret_cast<const __half2*>(&g);
+        const __half2* uh = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = __half22float2(gh[e]);
+            oh[e] = __hmul2(__floats2half2_rn(f.x / (1.0f + expf(-f.x)), f.y / (1.0f + expf(-f.y))), uh[e]);
+        }
+    } else if (p.x_op == SBVR_XOP_ADD_RMSNORM) {
+        uint4 a = __ldg(reinterpret_cast<const uint4*>(p.x + off));
+        __half2* ah = reinterpret_cast<__half2*>(&a);
+        if (p.delta) {
+            const uint4 b = __ldg(reinterpret_cast<const uint4*>(p.delta + off));
+            const __half2* bh = reinterpret_cast<const __half2*>(&b);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) ah[e] = __hadd2(ah[e], bh[e]);
+        }
+        if (p.h_out) *reinterpret_cast<uint4*>(p.h_out + off) = a;
+        const uint4 wv = __ldg(reinterpret_cast<const uint4*>(p.norm_w + (size_t)kb * 256 + lane * 8));
+        const __half2* wh = reinterpret_cast<const __half2*>(&wv);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = __half22float2(ah[e]);
+            oh[e] = __hmul2(wh[e], __floats2half2_rn(f.x * rs, f.y * rs));
+        }
+    } else {
+        o = __ldg(reinterpret_cast<const uint4*>(p.x + off));
+    }
+    unsigned char* ar = area[warp];
+    reinterpret_cast<uint4*>(ar)[lane] = o;
+    __syncwarp();
+    float* steps = reinterpret_cast<float*>(p.xq + (size_t)p.KB * p.M * 1024) + ((size_t)m * p.KB + kb) * NSUB;
+    xdigits_block<NSUB>(ar, steps, lane);
+    __syncwarp();
+    uint4* dst = reinterpret_cast<uint4*>(p.xq + ((size_t)kb * p.M + m) * 1024);
+    dst[lane] = reinterpret_cast<const uint4*>(ar)[lane];
+    dst[lane + 32] = reinterpret_cast<const uint4*>(ar)[lane + 32];
+}
+
+// ---------------------------------------------------------------------------------------------
+// bounded waits
+// ---------------------------------------------------------------------------------------------
+// Slow path of ts_wait: polls until the phase completes or about a second of SM clock has passed.  A time-out is
+// recorded in the status words and in the CTA's abort flag; the caller then carries on as if the phase had completed
+// (its results are garbage, the host sees SBVR_ERR_TIMEOUT), and every later wait of the CTA gives up at once, so
+// that the barrier protocol of the CTA runs to its end instead of hanging.
+__device__ __noinline__ void ts_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, unsigned int* status,
+                                          uint32_t where, bool heed_abort) {
+    const long long t0 = clock64();
+    for (;;) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.b32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (ok) return;
+        if (heed_abort && *abort_flag) return;
+        if (clock64() - t0 > 2000000000LL) {
+            *abort_flag = 1;
+            atomicExch(status, 1u);
+            atomicExch(status + 1, where);
+            return;
+        }
+    }
+}
+__device__ __forceinline__ void ts_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, unsigned int* status,
+                                        uint32_t where, bool heed_abort = true) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (!ok) ts_wait_slow(bar, parity, abort_flag, status, where, heed_abort);
+}
+
+// ---------------------------------------------------------------------------------------------
+// the product
+// ---------------------------------------------------------------------------------------------
+template <int S, int NSUB, int M, int IDXB>
+__global__ void __launch_bounds__(ts_threads(NSUB, M), 1)
+    linear_tcs_kernel(const __grid_constant__ CUtensorMap tmap, const TsParams p) {
+    pdl_launch_dependents();                       // the next kernel on the stream may be scheduled as SMs free up
+    extern __shared__ __align__(1024) unsigned char smem[];
+    constexpr int SP = ts_sp(S);
+    constexpr int TN = ts_tn(S);
+    constexpr int MPAD = ts_mpad(M);
+    constexpr int NMMA = 8 * MPAD;                 // MMA N: 8 digits per activation row
+    constexpr int DCOLS = ts_dcols(NSUB, M);       // columns of one D buffer
+    constexpr int WGCOLS = ts_wgcols(NSUB, M);     // A 2 x 32, D 2 x DCOLS
+    constexpr int NWG = ts_nwg(NSUB, M);
+    constexpr int CW0 = ts_cw0(NSUB, M);           // first compute warp
+    constexpr int WROW = TN * S * 4;               // bytes of one 32-k row of a stage
+    constexpr int CI_BYTES = (IDXB == 0) ? TN * S * 2 : TN * IDXB;     // coefficient data per group of a row tile
+    constexpr uint32_t STEP_TX = 8 * WROW + NSUB * CI_BYTES;
+    // instruction descriptor: A, B = E2M1 (1), scales UE8M0, M = 128, N = NMMA, K-major both, K = 64
+    constexpr uint32_t IDESC = (1u << 7) | (1u << 10) | ((uint32_t)(NMMA >> 3) << 17) | (1u << 23) | (8u << 24);
+
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem);                              // [NWG][TS_MAX_STAGES] stage landed
+    uint64_t* mma_bar = full + NWG * TS_MAX_STAGES;                                  // [NWG][2] MMAs of a step done
+    uint64_t* red_full = mma_bar + 2 * NWG;                                          // [2] sums of a segment deposited
+    uint64_t* red_empty = red_full + 2;                                              // [2] ... and consumed
+    uint64_t* b_ready = red_empty + 2;                                               // [1] digits copied
+    uint64_t* cache_bar = b_ready + 1;                                               // [1] codebook copied
+    uint64_t* tmem_ready = cache_bar + 1;                                            // [1] tensor memory allocated
+    uint64_t* sf_ready = tmem_ready + 1;                                             // [1] unit scale factors written
+    // [NWG][TS_MAX_STAGES] what the compute warps need to know about the step in a stage: k block | (deposit-up-to + 1) << 16
+    volatile uint32_t* steptab = reinterpret_cast<volatile uint32_t*>(smem + 512);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + TS_HDR - 64);  // a wait of this CTA ran out
+    uint32_t* tmem_base_s = reinterpret_cast<uint32_t*>(smem + TS_HDR - 16);
+
+    const int KB = p.KB, N = p.N;
+    float* red = reinterpret_cast<float*>(smem + p.off_red);                         // [2][NWG][M][128]
+    __half* cache_s = reinterpret_cast<__half*>(smem + p.off_cache);
+    unsigned char* ring = smem + p.off_ring;                                         // [NWG][stages][TS_STAGE_BYTES]
+    unsigned char* Bs = smem + p.off_b;                                              // [KB][M][1024], steps behind
+    const float* xsc = reinterpret_cast<const float*>(Bs + (size_t)KB * M * 1024);   // [M][KB * NSUB]
+    const int ST = p.stages;
+
+    // The warp index comes from a broadcast so that the compiler knows it (and everything derived from it: roles, tensor-memory
+    // addresses, barrier numbers, the operands of tcgen05.mma and of the TMA copies) to be warp-uniform and keeps it in uniform
+    // registers.  Measured: an MMA whose operands are formed in divergent code costs its issuer about 200 cycles, 13-17 otherwise.
+    const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
+    TsSegs sg;
+    sg.init((unsigned int)(p.NT * KB), gridDim.x, blockIdx.x, KB);
+    const int cta_steps = sg.b1 - sg.b0;
+
+    {
+        // one barrier per thread (they are contiguous): a single thread needed ~1 800 cycles for all of them
+        constexpr int NB_FULL = NWG * TS_MAX_STAGES, NB_MMA = 2 * NWG;
+        const int i = threadIdx.x;
+        if (i < NB_FULL + NB_MMA + 8) {
+            uint32_t count = 1u;                                                     // full, mma_bar, red_empty, cache, tmem
+            if (i >= NB_FULL + NB_MMA && i < NB_FULL + NB_MMA + 2) count = (uint32_t)(NWG * 4);            // red_full
+            if (i == NB_FULL + NB_MMA + 4) count = p.x_in_kernel ? (uint32_t)(NWG * 4) : 1u;               // b_ready
+            if (i == NB_FULL + NB_MMA + 7) count = 4u;                                                     // sf_ready
+            mbar_init(&full[i], count);
+            if (i == 0) *abort_flag = 0;
+            fence_mbar_init();
+        }
+    }
+    __syncthreads();                               // (A) barriers are initialised
+
+    const bool bulk_cache = p.cache_in_smem && ((p.C * S * 2) % 16 == 0);
+
+    if (warp == NWG) {
+        // ------------------------------ finisher warp ------------------------------
+        if (bulk_cache && lane == 0) {             // codebook -> shared memory, one asynchronous copy
+            mbar_arrive_expect_tx(cache_bar, (uint32_t)(p.C * S * 2));
+            bulk_g2s(cache_s, p.coeff, (uint32_t)(p.C * S * 2), cache_bar);
+        }
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_base_s)),
+                     "r"((uint32_t)TS_TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        ts_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tmem_ready);    // whoever needs tensor memory waits for this
+        pdl_wait();                                // digits, scratch and y belong to the stream's earlier kernels until now
+        if (lane == 0 && !p.x_in_kernel) {
+            mbar_arrive_expect_tx(b_ready, (uint32_t)p.xq_bytes);
+            bulk_g2s(Bs, p.xq, (uint32_t)p.xq_bytes, b_ready);
+        }
+        uint32_t fph = 0u;                         // bit b: phase of red_full[b]
+        const unsigned int T = (unsigned int)(p.NT * KB), Gd = gridDim.x;
+#pragma unroll 1
+        for (int q = 0; q < sg.nseg; ++q) {
+            const int ub = q & 1;
+            ts_wait(smem_u32(&red_full[ub]), (fph >> ub) & 1u, abort_flag, p.status, 0x330u);
+            fph ^= 1u << ub;
+            const int tile = sg.tile(q);
+            const int n0 = tile * TN;
+            const float* rs = red + (size_t)ub * NWG * M * 128;
+            constexpr int PER = (M * TN + 31) / 32;
+            float v[PER];
+#pragma unroll
+            for (int e = 0; e < PER; ++e) {
+                const int i = lane + 32 * e;
+                v[e] = 0.0f;
+                if (i < M * TN) {
+                    const int m = i / TN, nl = i % TN;
+#pragma unroll
+                    for (int j = 0; j < NWG; ++j)
+#pragma unroll
+                        for (int s = 0; s < SP; ++s) v[e] += rs[(j * M + m) * 128 + nl * SP + s];
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&red_empty[ub]);          // the warpgroups may deposit segment q + 2
+            bool fin = true;                                     // this CTA writes y for the tile
+            if (sg.shared(q)) {
+                // leave this CTA's part in scratch; whoever arrives last adds the parts in CTA order
+                const int slot = (tile == sg.tile_first) ? 0 : 1;
+                float* mine = p.partials + ((size_t)blockIdx.x * 2 + slot) * (M * TN);
+#pragma unroll
+                for (int e = 0; e < PER; ++e) {
+                    const int i = lane + 32 * e;
+                    if (i < M * TN) __stcg(mine + i, v[e]);
+                }
+                __threadfence();
+                __syncwarp();
+                const unsigned int s0 = (unsigned int)(tile * KB), s1 = s0 + KB - 1;
+                const int c_first = (int)(((s0 + 1u) * Gd - 1u) / T), c_last = (int)(((s1 + 1u) * Gd - 1u) / T);
+                unsigned int old = 0;
+                if (lane == 0) old = atomicAdd(p.counters + tile, 1u);
+                old = __shfl_sync(0xffffffffu, old, 0);
+                fin = (old == (unsigned int)(c_last - c_first));
+                if (fin) {
+                    __threadfence();
+#pragma unroll
+                    for (int e = 0; e < PER; ++e) v[e] = 0.0f;
+#pragma unroll 1
+                    for (int cc = c_first; cc <= c_last; ++cc) {
+                        const int cc_first_tile = (int)(((unsigned int)cc * T / Gd) / (unsigned int)KB);
+                        const int sl = (tile == cc_first_tile) ? 0 : 1;
+                        const float* part = p.partials + ((size_t)cc * 2 + sl) * (M * TN);
+#pragma unroll
+                        for (int e = 0; e < PER; ++e) {
+                            const int i = lane + 32 * e;
+                            if (i < M * TN) v[e] += __ldcg(part + i);
+                        }
+                    }
+                    if (lane == 0) p.counters[tile] = 0u;        // as the next call expects it
+                }
+            }
+            if (fin) {
+#pragma unroll
+                for (int e = 0; e < PER; ++e) {
+                    const int i = lane + 32 * e;
+                    if (i < M * TN) {
+                        const int m = i / TN, nl = i % TN;
+                        const float b = p.bias ? __half2float(p.bias[n0 + nl]) : 0.0f;
+                        p.y[(size_t)m * N + n0 + nl] = __float2half_rn(v[e] + b);
+                    }
+                }
+            }
+        }
+        if (lane == 0) {                           // the copies this warp asked for have landed before the CTA leaves
+            if (bulk_cache) ts_wait(smem_u32(cache_bar), 0u, abort_flag, p.status, 0x331u, false);
+            if (!p.x_in_kernel) ts_wait(smem_u32(b_ready), 0u, abort_flag, p.status, 0x332u, false);
+        }
+    } else if (warp < NWG) {
+        // ------------------------------ issuer warps ------------------------------
+        const int w = warp;
+        const int n_w = (cta_steps > w) ? (cta_steps - w + NWG - 1) / NWG : 0;     // steps of this warpgroup
+        const uint32_t ring_ws = smem_u32(ring + (size_t)w * ST * TS_STAGE_BYTES);
+        const uint32_t full_ws = smem_u32(full + w * TS_MAX_STAGES);
+        const unsigned char* cbytes_g = (IDXB == 0) ? reinterpret_cast<const unsigned char*>(p.coeff)
+                                                    : reinterpret_cast<const unsigned char*>(p.idx);
+        constexpr int CIROW_PER_N = (IDXB == 0) ? S * 2 : IDXB;                    // coefficient bytes per (group, row)
+        TsCursor lc;                               // the step whose loads are issued next
+        lc.start(sg, w);
+        int issued = 0, lslot = 0;
+        // Weights box + coefficient data of one step.  The whole (converged) warp forms the operands, one elected lane
+        // issues the copies.
+        auto load_step = [&]() {
+            const int tile = sg.tile(lc.q), kb = lc.k, q_i = lc.q;
+            lc.advance(sg, NWG);
+            const int q_next = lc.done(sg) ? sg.nseg : lc.q;
+            // after the sums of this step have been read, the warpgroup deposits its segments up to q_next (if it moves on)
+            const uint32_t entry = (uint32_t)kb | ((q_next != q_i) ? (uint32_t)(q_next + 1) << 16 : 0u);
+            const uint32_t stg = ring_ws + (uint32_t)lslot * TS_STAGE_BYTES;
+            const uint32_t bar = full_ws + (uint32_t)lslot * 8u;
+            const int c0 = tile * TN * S, c1 = kb * 8;
+            const unsigned char* csrc = cbytes_g + ((size_t)(kb * NSUB) * N + (size_t)tile * TN) * CIROW_PER_N;
+            if (elect_one()) {
+                steptab[w * TS_MAX_STAGES + lslot] = entry;      // published by the arrive below (release), read after the wait
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(STEP_TX) : "memory");
+                asm volatile(
+                    "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                    ::"r"(stg), "l"(reinterpret_cast<uint64_t>(&tmap)), "r"(c0), "r"(c1), "r"(bar)
+                    : "memory");
+#pragma unroll
+                for (int sub = 0; sub < NSUB; ++sub)
+                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                                     stg + TS_STAGE_WORDS + sub * CI_BYTES),
+                                 "l"(csrc + (size_t)sub * N * CIROW_PER_N), "r"((uint32_t)CI_BYTES), "r"(bar)
+                                 : "memory");
+            }
+            __syncwarp();
+            ++issued;
+            lslot = (lslot + 1 == ST) ? 0 : lslot + 1;
+        };
+        // weights do not depend on the previous kernel of the stream: the first stages are requested at once
+        {
+            const int first = n_w < ST ? n_w : ST;
+#pragma unroll 1
+            for (int i = 0; i < first; ++i) load_step();
+        }
+        ts_wait(smem_u32(tmem_ready), 0u, abort_flag, p.status, 0x312u);                  // tensor memory is allocated
+        ts_wait(smem_u32(sf_ready), 0u, abort_flag, p.status, 0x313u);                    // ... and holds the scale factors
+        ts_fence_after();
+        const uint32_t tbase = __shfl_sync(0xffffffffu, *tmem_base_s, 0);
+        if (n_w > 0) ts_wait(smem_u32(b_ready), 0u, abort_flag, p.status, 0x310u);        // the digits are in shared memory
+        const uint32_t sfa = tbase + TS_SF_COL, sfb = sfa;                    // every scale byte is 2^0
+        const uint32_t a_col = tbase + w * WGCOLS;
+        const uint32_t d_col = a_col + 64;
+        const uint64_t bdesc0 = ts_bdesc(smem_u32(Bs));
+        const uint32_t mbar0 = smem_u32(&mma_bar[w * 2]);
+        TsCursor mc;                               // the step whose MMAs are issued next
+        mc.start(sg, w);
+#pragma unroll 1
+        for (int i = 0; i < n_w; ++i) {
+            const int buf = i & 1;
+            const uint64_t bd = bdesc0 + (uint64_t)((uint32_t)(mc.k * M * 1024) >> 4);
+            const uint32_t dc = d_col + buf * DCOLS, ac = a_col + buf * 32;
+            named_bar_sync(1 + 2 * w + buf, 160);                             // A of step i is in tensor memory
+            ts_fence_after();
+            if (elect_one()) {
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    const int sub = (NSUB == 2) ? (q4 >> 1) : 0;
+                    const uint32_t accum = (NSUB == 2) ? (uint32_t)(q4 & 1) : (uint32_t)(q4 > 0);
+                    ts_mma(dc + sub * NMMA, ac + q4 * 8, bd + (uint64_t)((q4 * 256) >> 4), IDESC, sfa, sfb, accum);
+                }
+                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mbar0 + buf * 8)
+                             : "memory");
+            }
+            __syncwarp();
+            // every compute warp has read the stage of step i: refill it
+            if (issued < n_w) {
+                fence_proxy_async();
+                load_step();
+            }
+            mc.advance(sg, NWG);
+        }
+        if (lane == 0) {                           // no copy of this warp is in flight when the CTA leaves
+            const int firstj = issued > ST ? issued - ST : 0;
+#pragma unroll 1
+            for (int j = firstj; j < issued; ++j)
+                ts_wait(full_ws + (uint32_t)(j % ST) * 8u, (uint32_t)((j / ST) & 1), abort_flag, p.status, 0x311u, false);
+        }
+    } else if (warp < CW0) {
+        // ------------------------------ spare warps: nothing to do until the teardown ------------------------------
+    } else {
+        // ------------------------------ compute warpgroups ------------------------------
+        const int w = (warp - CW0) >> 2, wl = warp & 3;
+        const int r = wl * 32 + lane;              // MMA row = tensor-memory lane
+        const int nl = r / SP, s = r % SP;         // output row inside the tile, plane
+        const bool live_row = (S != 3) || (s < S);
+        const uint32_t lane_sel = (uint32_t)(wl * 32) << 16;
+        const int n_w = (cta_steps > w) ? (cta_steps - w + NWG - 1) / NWG : 0;
+        const unsigned char* ring_w = ring + (size_t)w * ST * TS_STAGE_BYTES;
+        const uint32_t full_ws = smem_u32(full + w * TS_MAX_STAGES);
+        const uint32_t mbar0 = smem_u32(&mma_bar[w * 2]);
+
+        if (p.cache_in_smem && !bulk_cache) {      // codebook whose byte size is not a multiple of 16: copy by hand
+            const int tid = threadIdx.x - CW0 * 32;
+            for (int i = tid; i < p.C * S; i += NWG * 128) cache_s[i] = p.coeff[i];
+        }
+        ts_wait(smem_u32(tmem_ready), 0u, abort_flag, p.status, 0x327u);                  // tensor memory is allocated
+        ts_fence_after();
+        const uint32_t tbase = __shfl_sync(0xffffffffu, *tmem_base_s, 0);
+        if (w == 0) {                              // unit scale factors, every byte 2^0
+            uint32_t f[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) f[i] = 0x7F7F7F7Fu;
+            ts_st32(tbase + lane_sel + TS_SF_COL, f);
+            ts_wait_st();
+            ts_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(sf_ready);  // the issuers wait for the four warps
+        }
+        if (p.cache_in_smem && !bulk_cache) named_bar_sync(15, NWG * 128);                // the hand-copied codebook is complete
+        if (p.x_in_kernel) {
+            // Short activation rows are quantised here, by every CTA for itself, one 256-k block per warp: cheaper than a
+            // launch of its own in front of this one (a kernel boundary costs more than the ~1 us this takes).
+            pdl_wait();                            // the activations belong to the stream's earlier kernels until now
+            float* xsc_w = reinterpret_cast<float*>(Bs + (size_t)KB * M * 1024);
+            // only the k blocks this CTA's steps touch: steps b0 .. b1-1 are k blocks (b0 + j) % KB, j < min(steps, KB)
+            const int nkb = cta_steps < KB ? cta_steps : KB;
+            for (int blk = warp - CW0; blk < M * nkb; blk += NWG * 4) {
+                const int m = blk / nkb, j = blk - m * nkb;
+                const int kb = (sg.b0 + j) % KB;
+                unsigned char* area = Bs + ((size_t)kb * M + m) * 1024;
+                reinterpret_cast<uint4*>(area)[lane] =
+                    __ldg(reinterpret_cast<const uint4*>(p.x + (size_t)m * p.K + (size_t)kb * 256) + lane);
+                __syncwarp();
+                xdigits_block<NSUB>(area, xsc_w + ((size_t)m * KB + kb) * NSUB, lane);
+            }
+            fence_proxy_async();                   // generic writes of the digits -> visible to the MMA's reads
+            __syncwarp();
+            if (lane == 0) mbar_arrive(b_ready);
+        }
+        if (bulk_cache) ts_wait(smem_u32(cache_bar), 0u, abort_flag, p.status, 0x320u);
+        ts_wait(smem_u32(b_ready), 0u, abort_flag, p.status, 0x321u);                      // digits and steps are in place
+
+        const uint32_t a_addr = tbase + w * WGCOLS + lane_sel;      // this thread's lane of the A buffers
+        const uint32_t d_addr = a_addr + 64;
+        float acc[M];
+#pragma unroll
+        for (int m = 0; m < M; ++m) acc[m] = 0.0f;
+        uint32_t eph = 0u;                         // bit b: phase of "sums consumed" barrier b
+        int qdep = 0;                              // next segment this warpgroup deposits
+
+        // This warpgroup's sums of segment qdep -> shared memory for the finisher; segments in which it has no step
+        // are deposited as zeros (the finisher counts every warp).
+        auto deposit_until = [&](int qnext) {
+#pragma unroll 1
+            while (qdep < qnext) {
+                const int ub = qdep & 1;
+                if (qdep >= 2) {                   // the finisher must have consumed segment qdep - 2
+                    ts_wait(smem_u32(&red_empty[ub]), (eph >> ub) & 1u, abort_flag, p.status, 0x322u);
+                    eph ^= 1u << ub;
+                }
+                float* rsd = red + (size_t)ub * NWG * M * 128;
+#pragma unroll
+                for (int m = 0; m < M; ++m) {
+                    rsd[(w * M + m) * 128 + r] = acc[m];
+                    acc[m] = 0.0f;
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&red_full[ub]);
+                ++qdep;
+            }
+        };
+        // non-blocking look at a barrier phase (1 = complete)
+        auto test = [](uint32_t bar, uint32_t parity) -> uint32_t {
+            uint32_t ok;
+            asm volatile(
+                "{\n\t.reg .pred p;\n\t"
+                "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                "selp.b32 %0, 1, 0, p;\n\t}"
+                : "=r"(ok)
+                : "r"(bar), "r"(parity)
+                : "memory");
+            return ok;
+        };
+
+        {
+            TsCursor cc;
+            cc.start(sg, w);
+            deposit_until(cc.done(sg) ? sg.nseg : cc.q);      // segments before this warpgroup's first step
+        }
+        float s1[NSUB][M], s2[NSUB][M];            // scales of steps i-1, i-2
+        int dep1 = -1, dep2 = -1;                  // deposit up to this segment after step i-1 / i-2 (-1: nothing)
+#pragma unroll
+        for (int sub = 0; sub < NSUB; ++sub)
+#pragma unroll
+            for (int m = 0; m < M; ++m) s1[sub][m] = s2[sub][m] = 0.0f;
+        const int wpos = nl * S + s;               // word of this thread's row inside a 32-k row of the stage
+        int slot = 0;                              // stage of step i
+        uint32_t fpar = 0u;                        // its parity
+        uint32_t okf = 0u, okm = 0u;               // the phases iteration i waits for were seen complete during iteration i - 1
+        // Iteration i loads, expands and hands over step i (if there is one) and reads the sums of step i - 2 (if there
+        // is one): the tensor pipe works two steps behind, and the loop body exists once.  Inside an iteration the
+        // independent latencies overlap: the tensor-memory read of step i - 2 is issued before the expansion of step i
+        // and consumed after it, and the barriers of iteration i + 1 are looked at while the stores of step i drain.
+#pragma unroll 1
+        for (int i = 0; i < n_w + 2; ++i) {
+            const int buf = i & 1;
+            const bool front = i < n_w, back = i >= 2;
+            uint32_t wv[8];
+            uint32_t craw[NSUB];                   // coefficient index (or the coefficient itself, direct form)
+            int kb = 0, dep_i = -1;
+            const unsigned char* stg = ring_w + (size_t)slot * TS_STAGE_BYTES;
+            if (front) {
+                // ---- the step's packed words and coefficient data have landed
+                if (!okf) ts_wait(full_ws + (uint32_t)slot * 8u, fpar, abort_flag, p.status, 0x323u);
+                const uint32_t entry = steptab[w * TS_MAX_STAGES + slot];
+                kb = (int)(entry & 0xFFFFu);
+                dep_i = (int)(entry >> 16) - 1;
+                const uint32_t* wsrc = reinterpret_cast<const uint32_t*>(stg) + wpos;
+#pragma unroll
+                for (int kw = 0; kw < 8; ++kw) wv[kw] = live_row ? wsrc[kw * (WROW / 4)] : 0u;
+#pragma unroll
+                for (int sub = 0; sub < NSUB; ++sub) {
+                    const unsigned char* cs = stg + TS_STAGE_WORDS + sub * CI_BYTES;
+                    if constexpr (IDXB == 0) craw[sub] = live_row ? (uint32_t)reinterpret_cast<const unsigned short*>(cs)[nl * S + s] : 0u;
+                    else if constexpr (IDXB == 1) craw[sub] = (uint32_t)cs[nl];
+                    else craw[sub] = (uint32_t)reinterpret_cast<const unsigned short*>(cs)[nl];
+                }
+            }
+            // ---- step i-2 is through the tensor pipe: its sums are requested, and A buffer i & 1 is free again
+            uint32_t d[NSUB][M][8];
+            if (back) {
+                if (!okm) ts_wait(mbar0 + buf * 8, (uint32_t)(((i >> 1) - 1) & 1), abort_flag, p.status, 0x324u);
+                ts_fence_after();
+#pragma unroll
+                for (int sub = 0; sub < NSUB; ++sub)
+#pragma unroll
+                    for (int m = 0; m < M; ++m) ts_ld8_issue(d_addr + buf * DCOLS + sub * NMMA + m * 8, d[sub][m]);
+            }
+            float scale[NSUB][M];
+            if (front) {
+#pragma unroll
+                for (int sub = 0; sub < NSUB; ++sub) {
+                    float c = 0.0f;
+                    if constexpr (IDXB == 0) {
+                        c = __half2float(__ushort_as_half((unsigned short)craw[sub]));
+                    } else {
+                        if (live_row) c = __half2float((p.cache_in_smem ? cache_s : p.coeff)[(size_t)craw[sub] * S + s]);
+                    }
+#pragma unroll
+                    for (int m = 0; m < M; ++m) scale[sub][m] = c * xsc[(m * KB + kb) * NSUB + sub];
+                }
+                // ---- packed words of this thread's row -> 32 words of 4-bit elements {0, 0.5 | 1 | 2 | 2}
+#pragma unroll
+                for (int h = 0; h < 4; ++h) {      // eight columns = one K = 64 MMA
+                    const uint32_t w0 = wv[2 * h], w1 = wv[2 * h + 1];
+                    ts_st8(a_addr + buf * 32 + h * 8, w0 & 0x11111111u, w0 & 0x22222222u, w0 & 0x44444444u,
+                           (w0 >> 1) & 0x44444444u, w1 & 0x11111111u, w1 & 0x22222222u, w1 & 0x44444444u,
+                           (w1 >> 1) & 0x44444444u);
+                }
+                if (++slot == ST) {
+                    slot = 0;
+                    fpar ^= 1u;
+                }
+            }
+            // ---- a look at the barriers of iteration i + 1 while the stores drain
+            okf = (i + 1 < n_w) ? test(full_ws + (uint32_t)slot * 8u, fpar) : 0u;
+            okm = (i + 1 >= 2) ? test(mbar0 + (buf ^ 1) * 8, (uint32_t)((((i + 1) >> 1) - 1) & 1)) : 0u;
+            if (back) {
+                // ---- D of step i-2 -> fp32 sums
+#pragma unroll
+                for (int sub = 0; sub < NSUB; ++sub)
+#pragma unroll
+                    for (int m = 0; m < M; ++m) ts_wait_ld(d[sub][m]);
+#pragma unroll
+                for (int sub = 0; sub < NSUB; ++sub)
+#pragma unroll
+                    for (int m = 0; m < M; ++m) {
+                        float pv = 0.0f;
+#pragma unroll
+                        for (int dg = 7; dg >= 0; --dg) pv = fmaf(pv, 4.0f, __uint_as_float(d[sub][m][dg]));
+                        acc[m] = fmaf(pv, s2[sub][m], acc[m]);
+                    }
+                if (dep2 >= 0) deposit_until(dep2);
+            }
+            if (front) {
+                ts_wait_st();
+                ts_fence_before();
+                ts_bar_arrive(1 + 2 * w + buf, 160);   // releases the issuer; also: the stage of step i has been read
+            }
+#pragma unroll
+            for (int sub = 0; sub < NSUB; ++sub)
+#pragma unroll
+                for (int m = 0; m < M; ++m) {
+                    s2[sub][m] = s1[sub][m];
+                    if (front) s1[sub][m] = scale[sub][m];
+                }
+            dep2 = dep1;
+            dep1 = dep_i;
+        }
+        deposit_until(sg.nseg);
+    }
+    // ------------------------------ teardown ------------------------------
+    ts_fence_before();
+    __syncthreads();
+    ts_fence_after();
+    if (warp == NWG)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(*tmem_base_s),
+                     "r"((uint32_t)TS_TMEM_COLS)
+                     : "memory");
+}
+
+// ---------------------------------------------------------------------------------------------
+// host
+// ---------------------------------------------------------------------------------------------
+struct TsPlan {
+    int KB, NT, grid, cache_in_smem, stages, smem;
+    int off_red, off_cache, off_ring, off_b;
+    int xq_bytes;
+    size_t partial_bytes;
+};
+
+static int ts_plan(const PackedW& w, int M, const DeviceInfo& di, TsPlan* pl) {
+    const int NSUB = 256 / w.G, TN = ts_tn(w.S);
+    const int NWG = ts_nwg(NSUB, M);
+    pl->KB = w.K / 256;
+    pl->NT = w.N / TN;
+    const long long T = (long long)pl->NT * pl->KB;
+    // Up to one row tile per SM: a CTA owns whole tiles and nothing is exchanged between CTAs (measured: the exchange at the
+    // end of a CTA that owns no whole tile costs 2.5-4.5 us).  More tiles than SMs: every SM takes the same number of
+    // steps; tiles that straddle CTAs are exchanged early, behind the whole tiles' work.
+    pl->grid = pl->NT <= di.sm_count ? pl->NT : di.sm_count;
+    pl->xq_bytes = ts_round_up(pl->KB * M * 1024 + M * pl->KB * NSUB * 4, 16);
+    pl->partial_bytes = (size_t)pl->grid * 2 * M * TN * sizeof(float);
+    const int red_bytes = 2 * NWG * M * 128 * 4;
+    const int cache_bytes = w.idx_bytes ? ts_round_up(w.C * w.S * 2, 16) : 0;
+    const int bbytes = pl->xq_bytes + TS_BSLACK;
+    auto layout = [&](int cb, int stages) {
+        pl->off_red = TS_HDR;
+        pl->off_cache = pl->off_red + red_bytes;
+        pl->off_ring = ts_round_up(pl->off_cache + cb, 128);
+        pl->off_b = ts_round_up(pl->off_ring + NWG * stages * TS_STAGE_BYTES, 1024);
+        return pl->off_b + bbytes;
+    };
+    // the codebook goes to shared memory if at least four stages per warpgroup still fit next to it
+    pl->cache_in_smem = (w.idx_bytes && cache_bytes <= 65536 && layout(cache_bytes, 4) <= di.smem_optin) ? 1 : 0;
+    const int cb = pl->cache_in_smem ? cache_bytes : 0;
+    int stages = TS_MAX_STAGES;
+    while (stages > 2 && layout(cb, stages) > di.smem_optin) --stages;
+    pl->stages = stages;
+    pl->smem = layout(cb, stages);
+    if (pl->smem > di.smem_optin) return SBVR_ERR_UNSUPPORTED;      // K * M too large for resident digits
+    return SBVR_OK;
+}
+
+bool linear_tcs_supported(const PackedW& w, int M) {
+    if (w.S < 2 || w.S > 4) return false;
+    if (w.G != 256 && w.G != 128) return false;
+    if (M < 1 || M > 4) return false;
+    if (w.N % ts_tn(w.S) || w.K % 256) return false;
+    if (w.idx_bytes < 0 || w.idx_bytes > 2) return false;
+    if (reinterpret_cast<uintptr_t>(w.coeff) & 15) return false;                 // bulk copies
+    if (reinterpret_cast<uintptr_t>(w.bvr) & 15) return false;                   // tensor map base
+    if (w.idx_bytes && (reinterpret_cast<uintptr_t>(w.idx) & 15)) return false;
+    if (w.N / ts_tn(w.S) > SBVR_WS_COUNTERS) return false;                       // one arrival counter per row tile
+    if ((size_t)(w.N / ts_tn(w.S)) * (size_t)(w.K / 256) >= ((size_t)1 << 24)) return false;   // 32-bit step arithmetic (steps x CTAs)
+    if ((size_t)w.N * w.S >= ((size_t)1 << 31)) return false;                    // 32-bit tensor coordinates
+    // the activation digits of the whole K stay resident in shared memory: K/256 * M KB, beside two stages at least
+    const int NSUB = 256 / w.G, KB = w.K / 256, NWG = ts_nwg(NSUB, M);
+    const int xq = ts_round_up(KB * M * 1024 + M * KB * NSUB * 4, 16);
+    const int need = ts_round_up(ts_round_up(TS_HDR + 2 * NWG * M * 128 * 4, 128) + NWG * 2 * TS_STAGE_BYTES, 1024) + xq +
+                     TS_BSLACK;
+    return need <= 227 * 1024;
+}
+
+size_t linear_tcs_workspace_bytes(const PackedW& w, int M, int sm_count) {
+    const int NSUB = 256 / w.G, TN = ts_tn(w.S), KB = w.K / 256;
+    const size_t xq = (size_t)ts_round_up(KB * M * 1024 + M * KB * NSUB * 4, 16);
+    return ((xq + 255) / 256) * 256 + (size_t)sm_count * 2 * M * TN * sizeof(float);
+}
+
+// ---- tensor maps of the packed words: uint32 [K/32 rows][N * S], box 8 rows x TN * S words
+typedef CUresult (*TsEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static int ts_tensor_map(const PackedW& w, CUtensorMap* out) {
+    static std::mutex mu;
+    static TsEncodeFn encode = nullptr;
+    struct Entry {
+        const void* bvr;
+        int N, K, S, valid;
+        CUtensorMap map;
+    };
+    static Entry cache[64];
+    std::lock_guard<std::mutex> lock(mu);
+    if (!encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        SBVR_CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+        if (!fn || qres != cudaDriverEntryPointSuccess) return SBVR_ERR_UNSUPPORTED;
+        encode = reinterpret_cast<TsEncodeFn>(fn);
+    }
+    const size_t h = (reinterpret_cast<uintptr_t>(w.bvr) >> 8) * 0x9E3779B97F4A7C15ull;
+    Entry& e = cache[(h >> 40) & 63];
+    if (!(e.valid && e.bvr == w.bvr && e.N == w.N && e.K == w.K && e.S == w.S)) {
+        const cuuint64_t dims[2] = {(cuuint64_t)w.N * w.S, (cuuint64_t)w.K / 32};
+        const cuuint64_t strides[1] = {(cuuint64_t)w.N * w.S * 4};
+        const cuuint32_t box[2] = {(cuuint32_t)(ts_tn(w.S) * w.S), 8u};
+        const cuuint32_t estr[2] = {1u, 1u};
+        const CUresult r = encode(&e.map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint32_t*>(w.bvr), dims, strides, box,
+                                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) {
+            e.valid = 0;
+            g_last_cuda_error = (int)r;
+            return SBVR_ERR_CUDA;
+        }
+        e.bvr = w.bvr, e.N = w.N, e.K = w.K, e.S = w.S, e.valid = 1;
+    }
+    *out = e.map;
+    return SBVR_OK;
+}
+
+template <int S, int NSUB, int M, int IDXB>
+static int ts_launch_inst(const CUtensorMap& tm, const TsParams& p, int grid, int smem, cudaStream_t st) {
+    static SmemOnce once;
+    const int rc = set_max_smem_once(once, linear_tcs_kernel<S, NSUB, M, IDXB>, 227 * 1024);
+    if (rc) return rc;
+    SBVR_CUDA_TRY(launch_pdl(linear_tcs_kernel<S, NSUB, M, IDXB>, dim3(grid), dim3(ts_threads(NSUB, M)), (size_t)smem, st, tm,
+                             p));
+    return SBVR_OK;
+}
+template <int S, int NSUB, int M>
+static int ts_launch_idx(const CUtensorMap& tm, const TsParams& p, int idxb, int grid, int smem, cudaStream_t st) {
+    switch (idxb) {
+        case 0: return ts_launch_inst<S, NSUB, M, 0>(tm, p, grid, smem, st);
+        case 1: return ts_launch_inst<S, NSUB, M, 1>(tm, p, grid, smem, st);
+        default: return ts_launch_inst<S, NSUB, M, 2>(tm, p, grid, smem, st);
+    }
+}
+template <int S, int NSUB>
+static int ts_launch_m(const CUtensorMap& tm, const TsParams& p, int M, int idxb, int grid, int smem, cudaStream_t st) {
+    switch (M) {
+        case 1: return ts_launch_idx<S, NSUB, 1>(tm, p, idxb, grid, smem, st);
+        case 2: return ts_launch_idx<S, NSUB, 2>(tm, p, idxb, grid, smem, st);
+        case 3: return ts_launch_idx<S, NSUB, 3>(tm, p, idxb, grid, smem, st);
+        default: return ts_launch_idx<S, NSUB, 4>(tm, p, idxb, grid, smem, st);
+    }
+}
+template <int S>
+static int ts_launch_g(const CUtensorMap& tm, const TsParams& p, int G, int M, int idxb, int grid, int smem,
+                       cudaStream_t st) {
+    return G == 256 ? ts_launch_m<S, 1>(tm, p, M, idxb, grid, smem, st) : ts_launch_m<S, 2>(tm, p, M, idxb, grid, smem, st);
+}
+
+// `scratch` (256-byte aligned, linear_tcs_workspace_bytes long), `status` and `counters` (one zeroed word per row
+// tile) are the caller's: the workspace form and the no-allocation form carve them differently.
+int launch_linear_tcs(const __half* x, const PackedW& w, const __half* bias, __half* y, int M, int device,
+                      unsigned int* status, unsigned int* counters, char* scratch, size_t scratch_bytes, cudaStream_t st,
+                      const XOp* xop) {
+    if (!linear_tcs_supported(w, M)) return SBVR_ERR_UNSUPPORTED;
+    if (!status || !counters || !scratch) return SBVR_ERR_WORKSPACE;
+    if (reinterpret_cast<uintptr_t>(x) & 15) return SBVR_ERR_ALIGN;      // x is fetched 16 bytes at a time
+    if (reinterpret_cast<uintptr_t>(scratch) & 255) return SBVR_ERR_ALIGN;
+    DeviceInfo di;
+    int rc = device_info(device, &di);
+    if (rc) return rc;
+    if (di.cc_major != 10) return SBVR_ERR_UNSUPPORTED;
+    TsPlan pl;
+    rc = ts_plan(w, M, di, &pl);
+    if (rc) return rc;
+    if (linear_tcs_workspace_bytes(w, M, di.sm_count) > scratch_bytes) return SBVR_ERR_WORKSPACE;
+    XqParams xp;
+    xp.x = x, xp.xq = reinterpret_cast<unsigned char*>(scratch), xp.K = w.K, xp.KB = pl.KB, xp.M = M;
+    xp.x_op = xop ? xop->op : SBVR_XOP_NONE;
+    xp.delta = xop ? xop->delta : nullptr, xp.norm_w = xop ? xop->norm_w : nullptr, xp.h_out = xop ? xop->h_out : nullptr;
+    xp.eps = xop ? xop->eps : 0.0f;
+    if (xp.x_op == SBVR_XOP_ADD_RMSNORM) {
+        // h_out is written while other blocks still read x and delta for the row's mean square
+        if (!xp.norm_w) return SBVR_ERR_BAD_ARG;
+        if (xp.h_out) {
+            const uintptr_t n = (uintptr_t)M * w.K * 2, ho = reinterpret_cast<uintptr_t>(xp.h_out);
+            auto overlaps = [&](const void* q) {
+                const uintptr_t a = reinterpret_cast<uintptr_t>(q);
+                return q && ho < a + n && a < ho + n;
+            };
+            if (overlaps(x) || overlaps(xp.delta)) return SBVR_ERR_BAD_ARG;
+        }
+        if ((reinterpret_cast<uintptr_t>(xp.delta) | reinterpret_cast<uintptr_t>(xp.norm_w) |
+             reinterpret_cast<uintptr_t>(xp.h_out)) & 15)
+            return SBVR_ERR_ALIGN;
+    }
+    CUtensorMap tm;
+    rc = ts_tensor_map(w, &tm);
+    if (rc) return rc;
+    // one block per compute warp at most: the CTAs quantise for themselves; longer rows (and rows with an op in front)
+    // get the separate kernel
+    const int NWG = ts_nwg(256 / w.G, M);
+    const bool in_kernel = (xp.x_op == SBVR_XOP_NONE) && (M * pl.KB <= NWG * 4);
+    if (!in_kernel) {
+        const dim3 qgrid((pl.KB + 15) / 16, M);
+        if (w.G == 256) SBVR_CUDA_TRY(launch_pdl(xquant_kernel<1>, qgrid, dim3(512), 0, st, xp));
+        else SBVR_CUDA_TRY(launch_pdl(xquant_kernel<2>, qgrid, dim3(512), 0, st, xp));
+    }
+    TsParams p;
+    p.x = x, p.x_in_kernel = in_kernel ? 1 : 0;
+    p.xq = xp.xq, p.idx = w.idx, p.coeff = w.coeff, p.bias = bias, p.y = y;
+    p.status = status, p.counters = counters;
+    p.partials = reinterpret_cast<float*>(scratch + ((size_t)pl.xq_bytes + 255) / 256 * 256);
+    p.N = w.N, p.K = w.K, p.KB = pl.KB, p.NT = pl.NT, p.C = w.C, p.cache_in_smem = pl.cache_in_smem, p.stages = pl.stages;
+    p.xq_bytes = pl.xq_bytes;
+    p.off_red = pl.off_red, p.off_cache = pl.off_cache, p.off_ring = pl.off_ring, p.off_b = pl.off_b;
+    switch (w.S) {
+        case 2: return ts_launch_g<2>(tm, p, w.G, M, w.idx_bytes, pl.grid, pl.smem, st);
+        case 3: return ts_launch_g<3>(tm, p, w.G, M, w.idx_bytes, pl.grid, pl.smem, st);
+        default: return ts_launch_g<4>(tm, p, w.G, M, w.idx_bytes, pl.grid, pl.smem, st);
+    }
+}
+
+}  // namespace sbvr

@@ -8,8 +8,9 @@
 // in global mode, where an allocation call would break that capture.  Such callers cannot create
 // the `sbvr_workspace_t` the regular entry point wants, because creating it is a cudaMalloc.
 //
-// What it does instead.  The scratch the kernels need (the time-out status word and the arrival
-// counters today; the array is sized for kernels that also keep partial sums there) lives in ONE
+// What it does instead.  The scratch the kernels need (the time-out status word, the arrival counters,
+// the quantised activations and partial sums of the decode kernel, the re-tiled activations and the
+// split-K partial sums of the batched kernel) lives in ONE
 // fixed array that is part of this library's device image, `g_noalloc_scratch` below: SBVR_NOALLOC_BYTES = 4 MiB per
 // GPU that loads the library, held until the process exits.  Nothing is allocated or freed here,
 // by this file or by anything it calls.
@@ -20,11 +21,14 @@
 //   * The array keeps what the previous call left.  The part that must be zero when a kernel starts
 //     (status word and arrival counters) is cleared on the stream at the beginning of every call.
 //   * The first call on each device looks up the array's device address (cudaGetSymbolAddress, which
-//     may load the module) and sets the kernels' shared-memory attribute.  Make that first call
-//     outside any stream capture, with the device current; later calls only enqueue work.
+//     may load the module); the first call of each kernel variant (S, G, M, index width) on a device sets
+//     that kernel's shared-memory attribute and may encode a tensor map.  Make such first calls outside
+//     any stream capture, with the device current; later calls only enqueue work.
 //   * A problem whose scratch does not fit is refused with SBVR_ERR_NOALLOC_LIMIT before anything is
-//     launched.  The decode kernel (M <= 4) keeps its sums and the quantised activations on the SM, so
-//     every shape it serves fits; shapes it does not serve run on the SIMT kernel, which needs no scratch.
+//     launched.  The decode kernel (M <= 4) needs about 4 K M bytes for the activation digits plus 150 KB of
+//     partial sums: every shape it serves fits.  Batches (M > 4) run on the tensor-core GEMM, whose re-tiled
+//     activations take M K 2 bytes (M rounded up to its tile): M = 128 at K = 14336 fits, M = 2048 does not
+//     and is refused.  Shapes neither kernel serves run on the SIMT kernel, which needs no scratch.
 //   * A time-out of a bounded device wait is recorded in the array but this entry point has no
 //     synchronising call to report it; use the workspace form if you need that.
 #include <mutex>
@@ -92,9 +96,6 @@ extern "C" int sbvr_linear_f16_noalloc(const void* x, const uint32_t* bvr, const
     DeviceInfo di;
     rc = device_info(dev, &di);
     if (rc) return rc;
-    if (di.cc_major != 10 || !linear_tc_supported(w, M) || (reinterpret_cast<uintptr_t>(x) & 15))
-        return launch_linear_simt(xh, w, bh, yh, M, st);      // this kernel needs no scratch at all
-
     // carve the static array exactly like an allocated workspace
     const size_t fixed = 256 + (size_t)SBVR_WS_COUNTERS * 4;
     sbvr_workspace ws;
@@ -106,9 +107,25 @@ extern "C" int sbvr_linear_f16_noalloc(const void* x, const uint32_t* bvr, const
     ws.dyn = ws.base + fixed;
     ws.dyn_bytes = SBVR_NOALLOC_BYTES - fixed;
     ws.pinned_status = nullptr;
+    const bool aligned_x = !(reinterpret_cast<uintptr_t>(x) & 15);
+    // which kernel serves the call, and how much of the array it needs
+    int kind = 0;                                  // 0: SIMT kernel (no scratch), 1: decode GEMV, 2: batched GEMM
+    size_t need = 0;
+    if (di.cc_major == 10 && aligned_x && linear_tcs_supported(w, M)) {
+        kind = 1;
+        need = linear_tcs_workspace_bytes(w, M, di.sm_count);       // activation digits + partial sums of shared row tiles
+    } else if (di.cc_major == 10 && linear_gemm_supported(w, M)) {
+        kind = 2;
+        need = linear_gemm_workspace_bytes(w, M, di.sm_count);      // re-tiled activations + fp32 parts of a split K
+    }
+    if (kind == 0) return launch_linear_simt(xh, w, bh, yh, M, st);
+    if (need > ws.dyn_bytes) return SBVR_ERR_NOALLOC_LIMIT;         // nothing has been launched
     // whatever the previous call (possibly an aborted one) left in the status word and the counters must go
     SBVR_CUDA_TRY(cudaMemsetAsync(ws.base, 0, fixed, st));
-    rc = launch_linear_tc(xh, w, bh, yh, M, &ws, st);
+    if (kind == 1)
+        rc = launch_linear_tcs(xh, w, bh, yh, M, dev, ws.status, ws.counters, ws.dyn, ws.dyn_bytes, st);
+    else
+        rc = launch_linear_gemm(xh, w, bh, yh, M, &ws, st);
     if (rc == SBVR_ERR_WORKSPACE) return SBVR_ERR_NOALLOC_LIMIT;
     return rc;
 }

@@ -115,13 +115,9 @@ static int popc_launch(const uint32_t* l_bvr, const void* l_idx, int lib, const 
     const size_t smem = (size_t)(K / 32) * PM_MT * LS * 4 + (size_t)(K / 256) * PM_MT * LS * 4 +
                         (size_t)PM_RB * PM_KQ * PM_MT * ROWS * 4;
     if (smem > 200 * 1024) return SBVR_ERR_UNSUPPORTED;
-    static int configured_for = -1;
-    int dev = 0;
-    SBVR_CUDA_TRY(cudaGetDevice(&dev));
-    if (configured_for != dev) {
-        SBVR_CUDA_TRY(cudaFuncSetAttribute(popc_mm_kernel<LS, RS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        configured_for = dev;
-    }
+    static SmemOnce once;
+    const int rc_once = set_max_smem_once(once, popc_mm_kernel<LS, RS>, 200 * 1024);
+    if (rc_once) return rc_once;
     const int blocks = (N + PM_RB * ROWS - 1) / (PM_RB * ROWS);
     for (int m0 = 0; m0 < M; m0 += PM_MT)
         SBVR_CUDA_TRY(launch_pdl(popc_mm_kernel<LS, RS>, dim3(blocks), dim3(PM_THREADS), smem, st, l_bvr, l_idx, lib, l_cache,

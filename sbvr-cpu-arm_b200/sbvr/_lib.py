@@ -130,6 +130,10 @@ class Workspace:
 
 
 _workspaces: dict = {}
+# Workspaces replaced by larger ones.  They are never freed: a captured CUDA graph keeps the raw pointers of the
+# workspace its kernels were recorded with (status word, counters, scratch), and would write into freed memory
+# on replay if the replaced allocation went back to the driver.
+_retired: list = []
 
 
 def workspace_bytes(device: int, M: int, N: int, K: int) -> int:
@@ -140,14 +144,12 @@ def workspace_bytes(device: int, M: int, N: int, K: int) -> int:
 
 def workspace(device: int, stream: int, nbytes: int = 0) -> Workspace:
     """One workspace per (device, stream): calls on one stream are ordered, so they may share scratch.
-    A workspace smaller than `nbytes` is replaced by a larger one (after the stream has drained)."""
+    A workspace smaller than `nbytes` is replaced by a larger one; the old one stays allocated for the life of the
+    process (graphs captured earlier on this stream still point into it)."""
     key = (device, stream)
     ws = _workspaces.get(key)
     if ws is not None and ws.nbytes < nbytes:
-        import torch
-        with torch.cuda.device(device):
-            torch.cuda.synchronize()
-        ws.close()
+        _retired.append(ws)
         ws = None
     if ws is None:
         ws = Workspace(device, max(nbytes, Workspace.DEFAULT_BYTES))
