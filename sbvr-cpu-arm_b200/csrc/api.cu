@@ -94,7 +94,7 @@ int sbvr_workspace_create(sbvr_workspace_t** out, int device, size_t bytes) {
     if (!out) return SBVR_ERR_BAD_ARG;
     *out = nullptr;
     if (bytes == 0) bytes = (size_t)32 << 20;
-    const size_t fixed = 256 + (size_t)SBVR_WS_COUNTERS * 4;
+    const size_t fixed = SBVR_WS_FIXED_BYTES;
     if (bytes < fixed + 4096) return SBVR_ERR_BAD_ARG;
     int prev = 0;
     SBVR_CUDA_TRY(cudaGetDevice(&prev));
@@ -118,6 +118,7 @@ int sbvr_workspace_create(sbvr_workspace_t** out, int device, size_t bytes) {
     }
     ws->status = reinterpret_cast<unsigned int*>(ws->base);
     ws->counters = reinterpret_cast<unsigned int*>(ws->base + 256);
+    ws->xchg = reinterpret_cast<unsigned long long*>(ws->base + 256 + (size_t)SBVR_WS_COUNTERS * 4);
     ws->dyn = ws->base + fixed;
     ws->dyn_bytes = bytes - fixed;
     *out = ws;                                     // the workspace exists whatever happens to the device switch below
@@ -133,7 +134,7 @@ int sbvr_workspace_bytes(int device, int M, int N, int K, size_t* bytes) {
     PackedW w;
     w.bvr = nullptr, w.idx = nullptr, w.coeff = nullptr, w.idx_bytes = 0, w.C = 0;
     w.N = N, w.K = K, w.S = 4, w.G = 256;
-    const size_t fixed = 256 + (size_t)SBVR_WS_COUNTERS * 4;
+    const size_t fixed = SBVR_WS_FIXED_BYTES;
     const size_t stage = (((size_t)M * K * 2 + 255) / 256 + ((size_t)M * N * 2 + 255) / 256) * 256;   // host-pointer staging
     *bytes = fixed + linear_gemm_workspace_bytes(w, M, di.sm_count) + stage + ((size_t)8 << 20);
     if (*bytes < ((size_t)32 << 20)) *bytes = (size_t)32 << 20;
@@ -160,7 +161,7 @@ int sbvr_workspace_status(sbvr_workspace_t* ws, sbvr_stream_t stream) {
     SBVR_CUDA_TRY(cudaStreamSynchronize(st));
     if (h[0] != 0) {
         // a kernel gave up: its arrival counters may be half-way; clear everything for the next call
-        SBVR_CUDA_TRY(cudaMemsetAsync(ws->base, 0, 256 + (size_t)SBVR_WS_COUNTERS * 4, st));
+        SBVR_CUDA_TRY(cudaMemsetAsync(ws->base, 0, SBVR_WS_FIXED_BYTES, st));
         SBVR_CUDA_TRY(cudaStreamSynchronize(st));
         return SBVR_ERR_TIMEOUT;
     }
@@ -202,7 +203,7 @@ int sbvr_linear_f16(const void* x, const uint32_t* bvr, const void* coeff_idx, i
     }
     if (algo == 2) {
         if (!ws) return SBVR_ERR_WORKSPACE;
-        return launch_linear_tcs(xh, w, bh, yh, M, ws->device, ws->status, ws->counters, ws->dyn, ws->dyn_bytes, st);
+        return launch_linear_tcs(xh, w, bh, yh, M, ws->device, ws->status, ws->xchg, ws->dyn, ws->dyn_bytes, st);
     }
     if (algo == 3) return launch_linear_gemm(xh, w, bh, yh, M, ws, st);
     return launch_linear_simt(xh, w, bh, yh, M, st);
@@ -230,7 +231,7 @@ int sbvr_linear_fused_f16(int x_op, const void* x, const void* delta, const void
     if (!linear_tcs_supported(w, M)) return SBVR_ERR_UNSUPPORTED;
     if (linear_tcs_workspace_bytes(w, M, di.sm_count) > ws->dyn_bytes) return SBVR_ERR_WORKSPACE;
     return launch_linear_tcs(reinterpret_cast<const __half*>(x), w, reinterpret_cast<const __half*>(bias),
-                             reinterpret_cast<__half*>(y), M, ws->device, ws->status, ws->counters, ws->dyn,
+                             reinterpret_cast<__half*>(y), M, ws->device, ws->status, ws->xchg, ws->dyn,
                              ws->dyn_bytes, reinterpret_cast<cudaStream_t>(stream), &xop);
 }
 

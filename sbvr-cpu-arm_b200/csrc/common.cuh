@@ -56,11 +56,15 @@ struct sbvr_workspace {
     // fixed regions at the start of `base`
     unsigned int* status;     // [4]   word 0: 0 ok / 1 a bounded wait ran out; word 1: where
     unsigned int* counters;   // [SBVR_WS_COUNTERS] reserved for kernels that count arrivals; all zero between calls
+    unsigned long long* xchg; // [SBVR_WS_XCHG_BYTES / 8] tagged exchange slots of the decode kernel; all zero between calls
     char* dyn;                // rest: staging buffers of the host-pointer entry point, future scratch
     size_t dyn_bytes;
     void* pinned_status;      // host, 16 bytes
 };
 #define SBVR_WS_COUNTERS 8192
+#define SBVR_WS_XCHG_BYTES (1u << 20)
+// bytes of the fixed regions in front of `dyn`: status (256), counters, exchange slots
+#define SBVR_WS_FIXED_BYTES (256u + SBVR_WS_COUNTERS * 4u + SBVR_WS_XCHG_BYTES)
 
 namespace sbvr {
 
@@ -109,12 +113,13 @@ struct XOp {
     __half* h_out;           // ADD_RMSNORM: x + delta is stored here (may be NULL; must not be x)
     float eps;
 };
-// The decode GEMV (linear_tcs.cu): FP4 tensor-core dot products, weights through TMA, work split by 256-k steps.  The caller hands it its scratch: a status word pair, one zeroed arrival counter per row
-// tile (SBVR_WS_COUNTERS at most) and `scratch_bytes` >= linear_tcs_workspace_bytes() of 256-byte aligned memory.
+// The decode GEMV (linear_tcs.cu): FP4 tensor-core dot products, weights through TMA, work split by 256-k steps.
+// The caller hands it its scratch: a status word pair, the zeroed exchange slots (SBVR_WS_XCHG_BYTES) and
+// `scratch_bytes` >= linear_tcs_workspace_bytes() of 256-byte aligned memory.
 bool linear_tcs_supported(const PackedW& w, int M);
 size_t linear_tcs_workspace_bytes(const PackedW& w, int M, int sm_count);
 int launch_linear_tcs(const __half* x, const PackedW& w, const __half* bias, __half* y, int M, int device,
-                      unsigned int* status, unsigned int* counters, char* scratch, size_t scratch_bytes, cudaStream_t st,
+                      unsigned int* status, unsigned long long* xchg, char* scratch, size_t scratch_bytes, cudaStream_t st,
                       const XOp* xop = nullptr);
 bool linear_gemm_supported(const PackedW& w, int M);
 size_t linear_gemm_workspace_bytes(const PackedW& w, int M, int sm_count);

@@ -19,10 +19,10 @@
 //   * The hand-over compute warps -> issuer is a named hardware barrier (bar.arrive / bar.sync), not an mbarrier poll.
 //   * Work is split by 256-k STEPS, not by row tiles: CTA c owns steps [c T / G, (c + 1) T / G) of the (row tile, k
 //     block) list, so every SM streams the same number of bytes whatever N / 32 mod #SM is.  A CTA's warpgroups take its
-//     steps round-robin.  Per row tile the warpgroups' sums meet in shared memory; a row tile that straddles CTAs is
-//     finished by the last CTA to arrive (partials in scratch, one counter per row tile, summed in CTA order, so the
-//     result is the same bits on every run).  Straddling tiles are processed first, so their exchange is over long
-//     before the CTA ends.
+//     steps round-robin.  Per row tile the warpgroups' sums meet in shared memory.  Every CTA owns NT / #CTA whole row
+//     tiles; the tiles left over are cut into steps and spread over the CTAs, and finished by the first CTA of each such
+//     tile, which collects the others' sums from tagged 8-byte slots in scratch in CTA order (the same bits on every
+//     run).  These shared parts are processed first, so their exchange is over long before the CTA ends.
 //   * Every wait is bounded; after a time-out a thread keeps the barrier protocol going but skips the work.
 //
 // Replaces cuda_1xtN_rd_WP8_TBW4_NS4 / cuda_row_deq_mm_T (reference sbvr/kernels/sbvr_kernel.cu:284-359, :121-191).
@@ -39,24 +39,29 @@ constexpr int TS_HDR = 1024;                    // barriers, flags, tensor-memor
 constexpr int TS_TMEM_COLS = 512;
 constexpr int TS_SF_COL = 480;                  // 32 columns of unit scale factors
 constexpr int TS_MAX_STAGES = 8;
-constexpr int TS_STAGE_WORDS = 4096;            // bytes of packed words per stage
-constexpr int TS_STAGE_BYTES = 4096 + 512;      // + coefficient indices / direct coefficients of the step
+constexpr int TS_STAGE_WORDS = 4096;            // bytes of packed words per 256-k block of a stage
 constexpr int TS_BSLACK = 4096;                 // MMA columns beyond M read (and ignore) what follows the digits
 
 __host__ __device__ constexpr int ts_sp(int S) { return S == 2 ? 2 : 4; }            // MMA rows per output row
 __host__ __device__ constexpr int ts_tn(int S) { return 128 / ts_sp(S); }            // output rows per tile
 __host__ __device__ constexpr int ts_mpad(int M) { return M <= 2 ? 2 : 4; }
-__host__ __device__ constexpr int ts_dcols(int NSUB, int M) { return NSUB * 8 * ts_mpad(M); }
-__host__ __device__ constexpr int ts_wgcols(int NSUB, int M) { return 64 + 2 * ts_dcols(NSUB, M); }
-__host__ __device__ constexpr int ts_nwg(int NSUB, int M) {
-    return (TS_SF_COL / ts_wgcols(NSUB, M)) > 5 ? 5 : (TS_SF_COL / ts_wgcols(NSUB, M));
+// KS = 256-k blocks per step (1 or 2).  Two blocks per step halve the per-step bookkeeping per weight byte; the sums of
+// the two blocks then share one 16-column D (block 0 in columns 0-7, block 1 in 8-15, see the MMA issue), which is only
+// possible for a single activation row and one group per block.
+__host__ __device__ constexpr int ts_dcols(int NSUB, int M, int KS) { return KS == 2 ? 16 : NSUB * 8 * ts_mpad(M); }
+__host__ __device__ constexpr int ts_wgcols(int NSUB, int M, int KS) { return 64 * KS + 2 * ts_dcols(NSUB, M, KS); }
+__host__ __device__ constexpr int ts_nwg(int NSUB, int M, int KS) {
+    return (TS_SF_COL / ts_wgcols(NSUB, M, KS)) > 5 ? 5 : (TS_SF_COL / ts_wgcols(NSUB, M, KS));
 }
+__host__ __device__ constexpr int ts_stage_bytes(int KS) { return KS * TS_STAGE_WORDS + 512; }   // + the step's coefficient data
 // Warp roles: warps 0 .. NWG-1 issue (MMAs and copies), warp NWG finishes, compute warps start at the next multiple of
 // four (a warp reaches the tensor-memory lanes 32 (warp % 4) ...).  The issuers have the lowest warp numbers on purpose:
 // the schedulers favour older warps, and an issuer behind twenty ALU-bound compute warps waited 700-1000 cycles for
 // its first issue slot after every hand-over.
-__host__ __device__ constexpr int ts_cw0(int NSUB, int M) { return (ts_nwg(NSUB, M) + 1 + 3) / 4 * 4; }
-__host__ __device__ constexpr int ts_threads(int NSUB, int M) { return (ts_cw0(NSUB, M) + 4 * ts_nwg(NSUB, M)) * 32; }
+__host__ __device__ constexpr int ts_cw0(int NSUB, int M, int KS) { return (ts_nwg(NSUB, M, KS) + 1 + 3) / 4 * 4; }
+__host__ __device__ constexpr int ts_threads(int NSUB, int M, int KS) {
+    return (ts_cw0(NSUB, M, KS) + 4 * ts_nwg(NSUB, M, KS)) * 32;
+}
 __host__ __device__ inline int ts_round_up(int v, int a) { return (v + a - 1) / a * a; }
 
 struct TsParams {
@@ -68,11 +73,10 @@ struct TsParams {
     const __half* bias;
     __half* y;
     unsigned int* status;
-    float* partials;              // [grid][2][M * TN]
-    unsigned int* counters;       // [NT], zero between calls
+    unsigned long long* xchg;     // [grid][2][M * TN] (fp32 sum | tag << 32) of the shared segments; all zero between calls
     int N, K, KB, NT, C, cache_in_smem, stages;
-    int xq_bytes;                 // bytes of the digits + steps, a multiple of 16
-    int off_red, off_cache, off_ring, off_b;      // shared-memory carve-up
+    int steps_bytes;              // bytes of the steps, rounded up to a multiple of 16
+    int off_red, off_cache, off_ring, off_b;      // shared-memory carve-up; at off_b: [1 KB zeros][digits][1 KB zeros][steps]
 };
 
 struct XqParams {
@@ -92,10 +96,10 @@ struct XqParams {
 __device__ __forceinline__ void ts_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void ts_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
-__device__ __forceinline__ uint64_t ts_bdesc(uint32_t saddr) {
+__device__ __forceinline__ uint64_t ts_bdesc(uint32_t saddr, uint32_t sbo = 1024u) {
     // K-major, no swizzle: core matrices of 8 rows x 16 B; 128 B between the two K chunks of one MMA,
-    // 1024 B between groups of 8 rows; descriptor version 1 (sm_100)
-    return (uint64_t)((saddr & 0x3FFFF) >> 4) | ((uint64_t)(128 >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
+    // `sbo` bytes between groups of 8 rows; descriptor version 1 (sm_100)
+    return (uint64_t)((saddr & 0x3FFFF) >> 4) | ((uint64_t)(128 >> 4) << 16) | ((uint64_t)(sbo >> 4) << 32) |
            ((uint64_t)1 << 46);
 }
 
@@ -138,6 +142,16 @@ __device__ __forceinline__ void ts_wait_ld(uint32_t (&r)[8]) {
                  : "memory");
 }
 
+// Sixteen columns of this thread's tensor-memory lane; valid after ts_wait_ld() on both halves.
+__device__ __forceinline__ void ts_ld16_issue(uint32_t taddr, uint32_t (&lo)[8], uint32_t (&hi)[8]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(lo[0]), "=r"(lo[1]), "=r"(lo[2]), "=r"(lo[3]), "=r"(lo[4]), "=r"(lo[5]), "=r"(lo[6]), "=r"(lo[7]), "=r"(hi[0]),
+          "=r"(hi[1]), "=r"(hi[2]), "=r"(hi[3]), "=r"(hi[4]), "=r"(hi[5]), "=r"(hi[6]), "=r"(hi[7])
+        : "r"(taddr)
+        : "memory");
+}
+
 // Eight columns of this thread's tensor-memory lane; the values are valid after ts_wait_ld().
 __device__ __forceinline__ void ts_ld8_issue(uint32_t taddr, uint32_t (&r)[8]) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
@@ -159,41 +173,42 @@ __device__ __forceinline__ void ts_bar_arrive(int id, int nthreads) {
 }
 
 // ---------------------------------------------------------------------------------------------
-// The list of 256-k steps of a CTA, in the order it processes them.
+// The steps of a CTA, in the order it processes them.
 //
-// Steps are numbered tile * KB + kb.  CTA c owns [b0, b1).  The row tiles it touches are `nseg` segments; the first
-// and the last may be shared with neighbouring CTAs (they do not cover the whole tile).  Shared segments come first.
+// A step is KS 256-k blocks of one row tile; a row tile has KBS steps.  With G CTAs and NT row tiles every CTA owns
+// base = NT / G WHOLE tiles (tiles c base .. c base + base - 1); the R = NT % G tiles left over are cut into their
+// R KBS steps, and CTA c takes steps [c R KBS / G, (c + 1) R KBS / G) of that list: one or two steps each, so every SM
+// gets the same work to within a step.  A CTA therefore has at most two "shared" segments (parts of left-over tiles,
+// finished together with other CTAs) and they come first, then its whole tiles.
 // ---------------------------------------------------------------------------------------------
 struct TsSegs {
-    int b0, b1, KB;
-    int tile_first, tile_last, nseg;
-    int H, L;                     // head / tail shared (only meaningful when nseg > 1; for nseg == 1, H = shared)
-    // T * G < 2^32 is checked by the host (linear_tcs_supported)
-    __host__ __device__ void init(unsigned int T, unsigned int G, unsigned int c, int KB_) {
-        KB = KB_;
-        b0 = (int)(c * T / G);
-        b1 = (int)((c + 1u) * T / G);
-        tile_first = b0 / KB;
-        tile_last = (b1 - 1) / KB;
-        nseg = (b1 > b0) ? tile_last - tile_first + 1 : 0;
-        H = (b0 % KB) != 0;
-        L = (b1 % KB) != 0;
-        if (nseg == 1) H = L = (b1 - b0 < KB);
+    int KBS, base, rem_tile0, own_tile0;
+    int r0, r1, rt_first, nrs, nseg, steps;
+    unsigned int RS, G;
+    // RS * G < 2^32 is checked by the host (linear_tcs_supported)
+    __host__ __device__ void init(int NT, int KBS_, unsigned int G_, unsigned int c) {
+        KBS = KBS_;
+        G = G_;
+        base = NT / (int)G;
+        const int R = NT - base * (int)G;
+        RS = (unsigned int)(R * KBS);
+        rem_tile0 = base * (int)G;
+        own_tile0 = (int)c * base;
+        r0 = (int)(c * RS / G);
+        r1 = (int)((c + 1u) * RS / G);
+        rt_first = r0 / KBS;
+        nrs = (r1 > r0) ? (r1 - 1) / KBS - rt_first + 1 : 0;
+        nseg = nrs + base;
+        steps = base * KBS + (r1 - r0);
     }
-    __host__ __device__ int tile(int q) const {
-        if (nseg <= 1 || !L) return tile_first + q;
-        if (q == H) return tile_last;
-        return q < H ? tile_first : tile_first + q - 1;
-    }
-    __host__ __device__ int k0(int q) const {
-        const int t = tile(q);
-        return (t == tile_first) ? b0 - t * KB : 0;
-    }
-    __host__ __device__ int k1(int q) const {
-        const int t = tile(q);
-        return (t == tile_last) ? b1 - t * KB : KB;
-    }
-    __host__ __device__ bool shared(int q) const { return k1(q) - k0(q) < KB; }
+    __host__ __device__ int tile(int q) const { return q < nrs ? rem_tile0 + rt_first + q : own_tile0 + (q - nrs); }
+    __host__ __device__ int k0(int q) const { return (q < nrs && q == 0) ? r0 - rt_first * KBS : 0; }
+    __host__ __device__ int k1(int q) const { return (q < nrs && q == nrs - 1) ? r1 - (rt_first + q) * KBS : KBS; }
+    __host__ __device__ bool shared(int q) const { return k1(q) - k0(q) < KBS; }
+    // the CTA that owns step r of the left-over list
+    __host__ __device__ int cta_of(unsigned int r) const { return (int)(((r + 1u) * G - 1u) / RS); }
+    // which of its two exchange slots CTA cc uses for left-over tile rt
+    __host__ __device__ int slot_of(unsigned int cc, int rt) const { return (rt == (int)(cc * RS / G) / KBS) ? 0 : 1; }
 };
 
 // Position in that list, advanced by a fixed stride (the number of warpgroups).
@@ -358,22 +373,28 @@ __device__ __forceinline__ void ts_wait(uint32_t bar, uint32_t parity, volatile 
 // ---------------------------------------------------------------------------------------------
 // the product
 // ---------------------------------------------------------------------------------------------
-template <int S, int NSUB, int M, int IDXB>
-__global__ void __launch_bounds__(ts_threads(NSUB, M), 1)
+template <int S, int NSUB, int M, int IDXB, int KS>
+__global__ void __launch_bounds__(ts_threads(NSUB, M, KS), 1)
     linear_tcs_kernel(const __grid_constant__ CUtensorMap tmap, const TsParams p) {
+    static_assert(KS == 1 || (KS == 2 && NSUB == 1 && M == 1), "two blocks per step: one activation row, one group per block");
     pdl_launch_dependents();                       // the next kernel on the stream may be scheduled as SMs free up
     extern __shared__ __align__(1024) unsigned char smem[];
     constexpr int SP = ts_sp(S);
     constexpr int TN = ts_tn(S);
     constexpr int MPAD = ts_mpad(M);
     constexpr int NMMA = 8 * MPAD;                 // MMA N: 8 digits per activation row
-    constexpr int DCOLS = ts_dcols(NSUB, M);       // columns of one D buffer
-    constexpr int WGCOLS = ts_wgcols(NSUB, M);     // A 2 x 32, D 2 x DCOLS
-    constexpr int NWG = ts_nwg(NSUB, M);
-    constexpr int CW0 = ts_cw0(NSUB, M);           // first compute warp
+    constexpr int DCOLS = ts_dcols(NSUB, M, KS);   // columns of one D buffer
+    constexpr int ACOLS = 32 * KS;                 // columns of one A buffer
+    constexpr int WGCOLS = ts_wgcols(NSUB, M, KS); // A 2 x ACOLS, D 2 x DCOLS
+    constexpr int NWG = ts_nwg(NSUB, M, KS);
+    constexpr int CW0 = ts_cw0(NSUB, M, KS);       // first compute warp
+    constexpr int NWARPS = CW0 + 4 * NWG;
+    constexpr int NGRP = KS * NSUB;                // coefficient groups per step
+    constexpr int STAGE_B = ts_stage_bytes(KS);
+    constexpr int COEF_OFF = KS * TS_STAGE_WORDS;  // the step's coefficient data inside a stage
     constexpr int WROW = TN * S * 4;               // bytes of one 32-k row of a stage
     constexpr int CI_BYTES = (IDXB == 0) ? TN * S * 2 : TN * IDXB;     // coefficient data per group of a row tile
-    constexpr uint32_t STEP_TX = 8 * WROW + NSUB * CI_BYTES;
+    constexpr uint32_t STEP_TX = KS * 8 * WROW + NGRP * CI_BYTES;
     // instruction descriptor: A, B = E2M1 (1), scales UE8M0, M = 128, N = NMMA, K-major both, K = 64
     constexpr uint32_t IDESC = (1u << 7) | (1u << 10) | ((uint32_t)(NMMA >> 3) << 17) | (1u << 23) | (8u << 24);
 
@@ -393,9 +414,12 @@ __global__ void __launch_bounds__(ts_threads(NSUB, M), 1)
     const int KB = p.KB, N = p.N;
     float* red = reinterpret_cast<float*>(smem + p.off_red);                         // [2][NWG][M][128]
     __half* cache_s = reinterpret_cast<__half*>(smem + p.off_cache);
-    unsigned char* ring = smem + p.off_ring;                                         // [NWG][stages][TS_STAGE_BYTES]
-    unsigned char* Bs = smem + p.off_b;                                              // [KB][M][1024], steps behind
-    const float* xsc = reinterpret_cast<const float*>(Bs + (size_t)KB * M * 1024);   // [M][KB * NSUB]
+    unsigned char* ring = smem + p.off_ring;                                         // [NWG][stages][STAGE_B]
+    unsigned char* Z0 = smem + p.off_b;                                              // 1 KB of zeros
+    unsigned char* Bs = Z0 + 1024;                                                   // [KB][M][1024] digits
+    unsigned char* Z1 = Bs + (size_t)KB * M * 1024;                                  // 1 KB of zeros
+    float* xsc = reinterpret_cast<float*>(Z1 + 1024);                                // [M][KB * NSUB] steps
+    const int KBS = KB / KS;                       // steps per row tile
     const int ST = p.stages;
 
     // The warp index comes from a broadcast so that the compiler knows it (and everything derived from it: roles, tensor-memory
@@ -403,8 +427,8 @@ __global__ void __launch_bounds__(ts_threads(NSUB, M), 1)
     // registers.  Measured: an MMA whose operands are formed in divergent code costs its issuer about 200 cycles, 13-17 otherwise.
     const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
     TsSegs sg;
-    sg.init((unsigned int)(p.NT * KB), gridDim.x, blockIdx.x, KB);
-    const int cta_steps = sg.b1 - sg.b0;
+    sg.init(p.NT, KBS, gridDim.x, blockIdx.x);
+    const int cta_steps = sg.steps;
 
     {
         // one barrier per thread (they are contiguous): a single thread needed ~1 800 cycles for all of them
@@ -413,7 +437,7 @@ __global__ void __launch_bounds__(ts_threads(NSUB, M), 1)
         if (i < NB_FULL + NB_MMA + 8) {
             uint32_t count = 1u;                                                     // full, mma_bar, red_empty, cache, tmem
             if (i >= NB_FULL + NB_MMA && i < NB_FULL + NB_MMA + 2) count = (uint32_t)(NWG * 4);            // red_full
-            if (i == NB_FULL + NB_MMA + 4) count = p.x_in_kernel ? (uint32_t)(NWG * 4) : 1u;               // b_ready
+            if (i == NB_FULL + NB_MMA + 4) count = (uint32_t)NWARPS + (p.x_in_kernel ? 0u : 1u);          // b_ready
             if (i == NB_FULL + NB_MMA + 7) count = 4u;                                                     // sf_ready
             mbar_init(&full[i], count);
             if (i == 0) *abort_flag = 0;
@@ -423,6 +447,39 @@ __global__ void __launch_bounds__(ts_threads(NSUB, M), 1)
     __syncthreads();                               // (A) barriers are initialised
 
     const bool bulk_cache = p.cache_in_smem && ((p.C * S * 2) % 16 == 0);
+
+    // Every warp of the CTA calls this once, when it has nothing else to do before the digits exist.  Short activation
+    // rows are quantised here, by every CTA for itself, one 256-k block per warp: cheaper than a launch of its own in
+    // front of this one (a kernel boundary costs more than the ~1 us this takes).  Only the k blocks this CTA's steps
+    // touch are done.  Either way the warp then reports on b_ready (its generic writes made visible to the MMA's reads).
+    auto digits_share = [&]() {
+        if (warp == CW0) {                         // the two zero blocks beside the digits
+            reinterpret_cast<uint4*>(Z0)[lane] = make_uint4(0u, 0u, 0u, 0u);
+            reinterpret_cast<uint4*>(Z0)[lane + 32] = make_uint4(0u, 0u, 0u, 0u);
+            reinterpret_cast<uint4*>(Z1)[lane] = make_uint4(0u, 0u, 0u, 0u);
+            reinterpret_cast<uint4*>(Z1)[lane + 32] = make_uint4(0u, 0u, 0u, 0u);
+        }
+        if (p.x_in_kernel) {
+            pdl_wait();                            // the activations belong to the stream's earlier kernels until now
+            // all k blocks if the CTA owns a whole tile, else the blocks of its one or two shared segments
+            int kb_lo = 0, nkb = KB;
+            if (sg.base == 0 && sg.nrs == 1) {
+                kb_lo = sg.k0(0) * KS;
+                nkb = (sg.k1(0) - sg.k0(0)) * KS;
+            }
+            for (int blk = warp; blk < M * nkb; blk += NWARPS) {
+                const int m = blk / nkb, kb = kb_lo + (blk - m * nkb);
+                unsigned char* area = Bs + ((size_t)kb * M + m) * 1024;
+                reinterpret_cast<uint4*>(area)[lane] =
+                    __ldg(reinterpret_cast<const uint4*>(p.x + (size_t)m * p.K + (size_t)kb * 256) + lane);
+                __syncwarp();
+                xdigits_block<NSUB>(area, xsc + ((size_t)m * KB + kb) * NSUB, lane);
+            }
+        }
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(b_ready);
+    };
 
     if (warp == NWG) {
         // ------------------------------ finisher warp ------------------------------
@@ -438,12 +495,14 @@ __global__ void __launch_bounds__(ts_threads(NSUB, M), 1)
         __syncwarp();
         if (lane == 0) mbar_arrive(tmem_ready);    // whoever needs tensor memory waits for this
         pdl_wait();                                // digits, scratch and y belong to the stream's earlier kernels until now
+        digits_share();
         if (lane == 0 && !p.x_in_kernel) {
-            mbar_arrive_expect_tx(b_ready, (uint32_t)p.xq_bytes);
-            bulk_g2s(Bs, p.xq, (uint32_t)p.xq_bytes, b_ready);
+            const uint32_t dig = (uint32_t)(KB * M * 1024);
+            mbar_arrive_expect_tx(b_ready, dig + (uint32_t)p.steps_bytes);
+            bulk_g2s(Bs, p.xq, dig, b_ready);
+            bulk_g2s(xsc, p.xq + dig, (uint32_t)p.steps_bytes, b_ready);
         }
         uint32_t fph = 0u;                         // bit b: phase of red_full[b]
-        const unsigned int T = (unsigned int)(p.NT * KB), Gd = gridDim.x;
 #pragma unroll 1
         for (int q = 0; q < sg.nseg; ++q) {
             const int ub = q & 1;
@@ -470,38 +529,86 @@ __global__ void __launch_bounds__(ts_threads(NSUB, M), 1)
             if (lane == 0) mbar_arrive(&red_empty[ub]);          // the warpgroups may deposit segment q + 2
             bool fin = true;                                     // this CTA writes y for the tile
             if (sg.shared(q)) {
-                // leave this CTA's part in scratch; whoever arrives last adds the parts in CTA order
-                const int slot = (tile == sg.tile_first) ? 0 : 1;
-                float* mine = p.partials + ((size_t)blockIdx.x * 2 + slot) * (M * TN);
+                // A left-over tile: its steps are spread over a few CTAs.  Every CTA but the first leaves its sums in its
+                // slot, each value in one 8-byte store with a tag beside it (no fence, no atomic, nothing to wait for);
+                // the first CTA collects the slots in CTA order as their tags appear, clears them, and writes y.
+                const int rt = tile - sg.rem_tile0;
+                const int c_first = sg.cta_of((unsigned int)(rt * KBS));
+                if ((int)blockIdx.x != c_first) {
+                    fin = false;
+                    unsigned long long* mine = p.xchg + ((size_t)blockIdx.x * 2 + sg.slot_of(blockIdx.x, rt)) * (M * TN);
 #pragma unroll
-                for (int e = 0; e < PER; ++e) {
-                    const int i = lane + 32 * e;
-                    if (i < M * TN) __stcg(mine + i, v[e]);
-                }
-                __threadfence();
-                __syncwarp();
-                const unsigned int s0 = (unsigned int)(tile * KB), s1 = s0 + KB - 1;
-                const int c_first = (int)(((s0 + 1u) * Gd - 1u) / T), c_last = (int)(((s1 + 1u) * Gd - 1u) / T);
-                unsigned int old = 0;
-                if (lane == 0) old = atomicAdd(p.counters + tile, 1u);
-                old = __shfl_sync(0xffffffffu, old, 0);
-                fin = (old == (unsigned int)(c_last - c_first));
-                if (fin) {
-                    __threadfence();
-#pragma unroll
-                    for (int e = 0; e < PER; ++e) v[e] = 0.0f;
-#pragma unroll 1
-                    for (int cc = c_first; cc <= c_last; ++cc) {
-                        const int cc_first_tile = (int)(((unsigned int)cc * T / Gd) / (unsigned int)KB);
-                        const int sl = (tile == cc_first_tile) ? 0 : 1;
-                        const float* part = p.partials + ((size_t)cc * 2 + sl) * (M * TN);
-#pragma unroll
-                        for (int e = 0; e < PER; ++e) {
-                            const int i = lane + 32 * e;
-                            if (i < M * TN) v[e] += __ldcg(part + i);
+                    for (int e = 0; e < PER; ++e) {
+                        const int i = lane + 32 * e;
+                        if (i < M * TN) {
+                            const unsigned long long pk = (unsigned long long)__float_as_uint(v[e]) | (1ull << 32);
+                            asm volatile("st.relaxed.gpu.global.b64 [%0], %1;" ::"l"(mine + i), "l"(pk) : "memory");
                         }
                     }
-                    if (lane == 0) p.counters[tile] = 0u;        // as the next call expects it
+                } else {
+                    // The contributors are the distinct owners of the tile's steps, in step order (not every CTA in
+                    // between owns a step of the left-over list).  Their slots are polled four contributors at a time, all
+                    // loads of a round in flight together: one dependent round trip per slot made a 16-way tile cost 30 us.
+                    int prev = c_first, k = 1;
+#pragma unroll 1
+                    while (k < KBS) {
+                        int ccs[4] = {0, 0, 0, 0}, n = 0;
+                        while (k < KBS && n < 4) {
+                            const int cc = sg.cta_of((unsigned int)(rt * KBS + k));
+                            ++k;
+                            if (cc != prev) {
+                                prev = cc;
+#pragma unroll
+                                for (int j = 0; j < 4; ++j)
+                                    if (j == n) ccs[j] = cc;
+                                ++n;
+                            }
+                        }
+                        unsigned long long pk[4][PER];
+                        const unsigned long long* slot[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            slot[j] = p.xchg + ((size_t)ccs[j] * 2 + sg.slot_of((unsigned int)ccs[j], rt)) * (M * TN);
+#pragma unroll
+                            for (int e = 0; e < PER; ++e) pk[j][e] = 0ull;
+                        }
+                        const long long t0 = clock64();
+                        for (;;) {
+                            bool missing = false;
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                                for (int e = 0; e < PER; ++e) {
+                                    const int i = lane + 32 * e;
+                                    if (j < n && i < M * TN && !(pk[j][e] >> 32))
+                                        asm volatile("ld.relaxed.gpu.global.b64 %0, [%1];" : "=l"(pk[j][e]) : "l"(slot[j] + i) : "memory");
+                                }
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                                for (int e = 0; e < PER; ++e) {
+                                    const int i = lane + 32 * e;
+                                    if (j < n && i < M * TN && !(pk[j][e] >> 32)) missing = true;
+                                }
+                            if (!missing || *abort_flag) break;
+                            if (clock64() - t0 > 2000000000LL) {              // a contributor never delivered
+                                *abort_flag = 1;
+                                atomicExch(p.status, 1u);
+                                atomicExch(p.status + 1, 0x340u);
+                                break;
+                            }
+                        }
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+#pragma unroll
+                            for (int e = 0; e < PER; ++e) {
+                                const int i = lane + 32 * e;
+                                if (j < n && i < M * TN) {
+                                    v[e] += __uint_as_float((unsigned int)pk[j][e]);
+                                    asm volatile("st.relaxed.gpu.global.b64 [%0], %1;" ::"l"(slot[j] + i), "l"(0ull) : "memory");
+                                }
+                            }
+                    }
                 }
             }
             if (fin) {
@@ -518,13 +625,13 @@ __global__ void __launch_bounds__(ts_threads(NSUB, M), 1)
         }
         if (lane == 0) {                           // the copies this warp asked for have landed before the CTA leaves
             if (bulk_cache) ts_wait(smem_u32(cache_bar), 0u, abort_flag, p.status, 0x331u, false);
-            if (!p.x_in_kernel) ts_wait(smem_u32(b_ready), 0u, abort_flag, p.status, 0x332u, false);
+            ts_wait(smem_u32(b_ready), 0u, abort_flag, p.status, 0x332u, false);
         }
     } else if (warp < NWG) {
         // ------------------------------ issuer warps ------------------------------
         const int w = warp;
         const int n_w = (cta_steps > w) ? (cta_steps - w + NWG - 1) / NWG : 0;     // steps of this warpgroup
-        const uint32_t ring_ws = smem_u32(ring + (size_t)w * ST * TS_STAGE_BYTES);
+        const uint32_t ring_ws = smem_u32(ring + (size_t)w * ST * STAGE_B);
         const uint32_t full_ws = smem_u32(full + w * TS_MAX_STAGES);
         const unsigned char* cbytes_g = (IDXB == 0) ? reinterpret_cast<const unsigned char*>(p.coeff)
                                                     : reinterpret_cast<const unsigned char*>(p.idx);
@@ -535,12 +642,12 @@ __global__ void __launch_bounds__(ts_threads(NSUB, M), 1)
         // Weights box + coefficient data of one step.  The whole (converged) warp forms the operands, one elected lane
         // issues the copies.
         auto load_step = [&]() {
-            const int tile = sg.tile(lc.q), kb = lc.k, q_i = lc.q;
+            const int tile = sg.tile(lc.q), kb = lc.k * KS, q_i = lc.q;
             lc.advance(sg, NWG);
             const int q_next = lc.done(sg) ? sg.nseg : lc.q;
             // after the sums of this step have been read, the warpgroup deposits its segments up to q_next (if it moves on)
             const uint32_t entry = (uint32_t)kb | ((q_next != q_i) ? (uint32_t)(q_next + 1) << 16 : 0u);
-            const uint32_t stg = ring_ws + (uint32_t)lslot * TS_STAGE_BYTES;
+            const uint32_t stg = ring_ws + (uint32_t)lslot * STAGE_B;
             const uint32_t bar = full_ws + (uint32_t)lslot * 8u;
             const int c0 = tile * TN * S, c1 = kb * 8;
             const unsigned char* csrc = cbytes_g + ((size_t)(kb * NSUB) * N + (size_t)tile * TN) * CIROW_PER_N;
@@ -552,9 +659,9 @@ __global__ void __launch_bounds__(ts_threads(NSUB, M), 1)
                     ::"r"(stg), "l"(reinterpret_cast<uint64_t>(&tmap)), "r"(c0), "r"(c1), "r"(bar)
                     : "memory");
 #pragma unroll
-                for (int sub = 0; sub < NSUB; ++sub)
+                for (int sub = 0; sub < NGRP; ++sub)
                     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                                     stg + TS_STAGE_WORDS + sub * CI_BYTES),
+                                     stg + COEF_OFF + sub * CI_BYTES),
                                  "l"(csrc + (size_t)sub * N * CIROW_PER_N), "r"((uint32_t)CI_BYTES), "r"(bar)
                                  : "memory");
             }
@@ -568,6 +675,7 @@ __global__ void __launch_bounds__(ts_threads(NSUB, M), 1)
 #pragma unroll 1
             for (int i = 0; i < first; ++i) load_step();
         }
+        digits_share();
         ts_wait(smem_u32(tmem_ready), 0u, abort_flag, p.status, 0x312u);                  // tensor memory is allocated
         ts_wait(smem_u32(sf_ready), 0u, abort_flag, p.status, 0x313u);                    // ... and holds the scale factors
         ts_fence_after();
@@ -575,24 +683,40 @@ __global__ void __launch_bounds__(ts_threads(NSUB, M), 1)
         if (n_w > 0) ts_wait(smem_u32(b_ready), 0u, abort_flag, p.status, 0x310u);        // the digits are in shared memory
         const uint32_t sfa = tbase + TS_SF_COL, sfb = sfa;                    // every scale byte is 2^0
         const uint32_t a_col = tbase + w * WGCOLS;
-        const uint32_t d_col = a_col + 64;
-        const uint64_t bdesc0 = ts_bdesc(smem_u32(Bs));
+        const uint32_t d_col = a_col + 2 * ACOLS;
+        const uint32_t bs0 = smem_u32(Bs), z0 = smem_u32(Z0), z1 = smem_u32(Z1);
+        const uint64_t bdesc0 = ts_bdesc(bs0);
         const uint32_t mbar0 = smem_u32(&mma_bar[w * 2]);
         TsCursor mc;                               // the step whose MMAs are issued next
         mc.start(sg, w);
 #pragma unroll 1
         for (int i = 0; i < n_w; ++i) {
             const int buf = i & 1;
-            const uint64_t bd = bdesc0 + (uint64_t)((uint32_t)(mc.k * M * 1024) >> 4);
-            const uint32_t dc = d_col + buf * DCOLS, ac = a_col + buf * 32;
+            const int kb = mc.k * KS;
+            const uint64_t bd = bdesc0 + (uint64_t)((uint32_t)(kb * M * 1024) >> 4);
+            const uint32_t dc = d_col + buf * DCOLS, ac = a_col + buf * ACOLS;
+            // Two blocks per step: block 0 multiplies [digits of kb | zeros] (rows 8-15 of B point at the zero block behind
+            // the digits), block 1 multiplies [zeros | digits of kb + 1] (rows 0-7 are the zero block in front): the first
+            // MMA overwrites all 16 columns, the others accumulate, and the two blocks' sums end up side by side.
+            const uint32_t x0 = bs0 + (uint32_t)kb * 1024u, x1 = x0 + 1024u;
+            const uint64_t bd_a = ts_bdesc(x0, z1 - x0), bd_b = ts_bdesc(z0, x1 - z0);
             named_bar_sync(1 + 2 * w + buf, 160);                             // A of step i is in tensor memory
             ts_fence_after();
             if (elect_one()) {
+                if constexpr (KS == 2) {
 #pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    const int sub = (NSUB == 2) ? (q4 >> 1) : 0;
-                    const uint32_t accum = (NSUB == 2) ? (uint32_t)(q4 & 1) : (uint32_t)(q4 > 0);
-                    ts_mma(dc + sub * NMMA, ac + q4 * 8, bd + (uint64_t)((q4 * 256) >> 4), IDESC, sfa, sfb, accum);
+                    for (int q4 = 0; q4 < 4; ++q4)
+                        ts_mma(dc, ac + q4 * 8, bd_a + (uint64_t)((q4 * 256) >> 4), IDESC, sfa, sfb, (uint32_t)(q4 > 0));
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4)
+                        ts_mma(dc, ac + 32 + q4 * 8, bd_b + (uint64_t)((q4 * 256) >> 4), IDESC, sfa, sfb, 1u);
+                } else {
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        const int sub = (NSUB == 2) ? (q4 >> 1) : 0;
+                        const uint32_t accum = (NSUB == 2) ? (uint32_t)(q4 & 1) : (uint32_t)(q4 > 0);
+                        ts_mma(dc + sub * NMMA, ac + q4 * 8, bd + (uint64_t)((q4 * 256) >> 4), IDESC, sfa, sfb, accum);
+                    }
                 }
                 asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mbar0 + buf * 8)
                              : "memory");
@@ -612,7 +736,8 @@ __global__ void __launch_bounds__(ts_threads(NSUB, M), 1)
                 ts_wait(full_ws + (uint32_t)(j % ST) * 8u, (uint32_t)((j / ST) & 1), abort_flag, p.status, 0x311u, false);
         }
     } else if (warp < CW0) {
-        // ------------------------------ spare warps: nothing to do until the teardown ------------------------------
+        // ------------------------------ spare warps: their share of the digits, then nothing until the teardown ----
+        digits_share();
     } else {
         // ------------------------------ compute warpgroups ------------------------------
         const int w = (warp - CW0) >> 2, wl = warp & 3;
@@ -621,7 +746,7 @@ __global__ void __launch_bounds__(ts_threads(NSUB, M), 1)
         const bool live_row = (S != 3) || (s < S);
         const uint32_t lane_sel = (uint32_t)(wl * 32) << 16;
         const int n_w = (cta_steps > w) ? (cta_steps - w + NWG - 1) / NWG : 0;
-        const unsigned char* ring_w = ring + (size_t)w * ST * TS_STAGE_BYTES;
+        const unsigned char* ring_w = ring + (size_t)w * ST * STAGE_B;
         const uint32_t full_ws = smem_u32(full + w * TS_MAX_STAGES);
         const uint32_t mbar0 = smem_u32(&mma_bar[w * 2]);
 
@@ -643,31 +768,12 @@ __global__ void __launch_bounds__(ts_threads(NSUB, M), 1)
             if (lane == 0) mbar_arrive(sf_ready);  // the issuers wait for the four warps
         }
         if (p.cache_in_smem && !bulk_cache) named_bar_sync(15, NWG * 128);                // the hand-copied codebook is complete
-        if (p.x_in_kernel) {
-            // Short activation rows are quantised here, by every CTA for itself, one 256-k block per warp: cheaper than a
-            // launch of its own in front of this one (a kernel boundary costs more than the ~1 us this takes).
-            pdl_wait();                            // the activations belong to the stream's earlier kernels until now
-            float* xsc_w = reinterpret_cast<float*>(Bs + (size_t)KB * M * 1024);
-            // only the k blocks this CTA's steps touch: steps b0 .. b1-1 are k blocks (b0 + j) % KB, j < min(steps, KB)
-            const int nkb = cta_steps < KB ? cta_steps : KB;
-            for (int blk = warp - CW0; blk < M * nkb; blk += NWG * 4) {
-                const int m = blk / nkb, j = blk - m * nkb;
-                const int kb = (sg.b0 + j) % KB;
-                unsigned char* area = Bs + ((size_t)kb * M + m) * 1024;
-                reinterpret_cast<uint4*>(area)[lane] =
-                    __ldg(reinterpret_cast<const uint4*>(p.x + (size_t)m * p.K + (size_t)kb * 256) + lane);
-                __syncwarp();
-                xdigits_block<NSUB>(area, xsc_w + ((size_t)m * KB + kb) * NSUB, lane);
-            }
-            fence_proxy_async();                   // generic writes of the digits -> visible to the MMA's reads
-            __syncwarp();
-            if (lane == 0) mbar_arrive(b_ready);
-        }
+        digits_share();
         if (bulk_cache) ts_wait(smem_u32(cache_bar), 0u, abort_flag, p.status, 0x320u);
         ts_wait(smem_u32(b_ready), 0u, abort_flag, p.status, 0x321u);                      // digits and steps are in place
 
         const uint32_t a_addr = tbase + w * WGCOLS + lane_sel;      // this thread's lane of the A buffers
-        const uint32_t d_addr = a_addr + 64;
+        const uint32_t d_addr = a_addr + 2 * ACOLS;
         float acc[M];
 #pragma unroll
         for (int m = 0; m < M; ++m) acc[m] = 0.0f;
@@ -713,10 +819,10 @@ __global__ void __launch_bounds__(ts_threads(NSUB, M), 1)
             cc.start(sg, w);
             deposit_until(cc.done(sg) ? sg.nseg : cc.q);      // segments before this warpgroup's first step
         }
-        float s1[NSUB][M], s2[NSUB][M];            // scales of steps i-1, i-2
+        float s1[NGRP][M], s2[NGRP][M];            // scales of steps i-1, i-2
         int dep1 = -1, dep2 = -1;                  // deposit up to this segment after step i-1 / i-2 (-1: nothing)
 #pragma unroll
-        for (int sub = 0; sub < NSUB; ++sub)
+        for (int sub = 0; sub < NGRP; ++sub)
 #pragma unroll
             for (int m = 0; m < M; ++m) s1[sub][m] = s2[sub][m] = 0.0f;
         const int wpos = nl * S + s;               // word of this thread's row inside a 32-k row of the stage
@@ -731,10 +837,10 @@ __global__ void __launch_bounds__(ts_threads(NSUB, M), 1)
         for (int i = 0; i < n_w + 2; ++i) {
             const int buf = i & 1;
             const bool front = i < n_w, back = i >= 2;
-            uint32_t wv[8];
-            uint32_t craw[NSUB];                   // coefficient index (or the coefficient itself, direct form)
+            uint32_t wv[8 * KS];
+            uint32_t craw[NGRP];                   // coefficient index (or the coefficient itself, direct form)
             int kb = 0, dep_i = -1;
-            const unsigned char* stg = ring_w + (size_t)slot * TS_STAGE_BYTES;
+            const unsigned char* stg = ring_w + (size_t)slot * STAGE_B;
             if (front) {
                 // ---- the step's packed words and coefficient data have landed
                 if (!okf) ts_wait(full_ws + (uint32_t)slot * 8u, fpar, abort_flag, p.status, 0x323u);
@@ -743,29 +849,33 @@ __global__ void __launch_bounds__(ts_threads(NSUB, M), 1)
                 dep_i = (int)(entry >> 16) - 1;
                 const uint32_t* wsrc = reinterpret_cast<const uint32_t*>(stg) + wpos;
 #pragma unroll
-                for (int kw = 0; kw < 8; ++kw) wv[kw] = live_row ? wsrc[kw * (WROW / 4)] : 0u;
+                for (int kw = 0; kw < 8 * KS; ++kw) wv[kw] = live_row ? wsrc[kw * (WROW / 4)] : 0u;
 #pragma unroll
-                for (int sub = 0; sub < NSUB; ++sub) {
-                    const unsigned char* cs = stg + TS_STAGE_WORDS + sub * CI_BYTES;
+                for (int sub = 0; sub < NGRP; ++sub) {
+                    const unsigned char* cs = stg + COEF_OFF + sub * CI_BYTES;
                     if constexpr (IDXB == 0) craw[sub] = live_row ? (uint32_t)reinterpret_cast<const unsigned short*>(cs)[nl * S + s] : 0u;
                     else if constexpr (IDXB == 1) craw[sub] = (uint32_t)cs[nl];
                     else craw[sub] = (uint32_t)reinterpret_cast<const unsigned short*>(cs)[nl];
                 }
             }
             // ---- step i-2 is through the tensor pipe: its sums are requested, and A buffer i & 1 is free again
-            uint32_t d[NSUB][M][8];
+            uint32_t d[NGRP][M][8];
             if (back) {
                 if (!okm) ts_wait(mbar0 + buf * 8, (uint32_t)(((i >> 1) - 1) & 1), abort_flag, p.status, 0x324u);
                 ts_fence_after();
+                if constexpr (KS == 2) {
+                    ts_ld16_issue(d_addr + buf * DCOLS, d[0][0], d[1][0]);
+                } else {
 #pragma unroll
-                for (int sub = 0; sub < NSUB; ++sub)
+                    for (int sub = 0; sub < NSUB; ++sub)
 #pragma unroll
-                    for (int m = 0; m < M; ++m) ts_ld8_issue(d_addr + buf * DCOLS + sub * NMMA + m * 8, d[sub][m]);
+                        for (int m = 0; m < M; ++m) ts_ld8_issue(d_addr + buf * DCOLS + sub * NMMA + m * 8, d[sub][m]);
+                }
             }
-            float scale[NSUB][M];
+            float scale[NGRP][M];
             if (front) {
 #pragma unroll
-                for (int sub = 0; sub < NSUB; ++sub) {
+                for (int sub = 0; sub < NGRP; ++sub) {
                     float c = 0.0f;
                     if constexpr (IDXB == 0) {
                         c = __half2float(__ushort_as_half((unsigned short)craw[sub]));
@@ -777,9 +887,9 @@ __global__ void __launch_bounds__(ts_threads(NSUB, M), 1)
                 }
                 // ---- packed words of this thread's row -> 32 words of 4-bit elements {0, 0.5 | 1 | 2 | 2}
 #pragma unroll
-                for (int h = 0; h < 4; ++h) {      // eight columns = one K = 64 MMA
+                for (int h = 0; h < 4 * KS; ++h) { // eight columns = one K = 64 MMA
                     const uint32_t w0 = wv[2 * h], w1 = wv[2 * h + 1];
-                    ts_st8(a_addr + buf * 32 + h * 8, w0 & 0x11111111u, w0 & 0x22222222u, w0 & 0x44444444u,
+                    ts_st8(a_addr + buf * ACOLS + h * 8, w0 & 0x11111111u, w0 & 0x22222222u, w0 & 0x44444444u,
                            (w0 >> 1) & 0x44444444u, w1 & 0x11111111u, w1 & 0x22222222u, w1 & 0x44444444u,
                            (w1 >> 1) & 0x44444444u);
                 }
@@ -794,11 +904,11 @@ __global__ void __launch_bounds__(ts_threads(NSUB, M), 1)
             if (back) {
                 // ---- D of step i-2 -> fp32 sums
 #pragma unroll
-                for (int sub = 0; sub < NSUB; ++sub)
+                for (int sub = 0; sub < NGRP; ++sub)
 #pragma unroll
                     for (int m = 0; m < M; ++m) ts_wait_ld(d[sub][m]);
 #pragma unroll
-                for (int sub = 0; sub < NSUB; ++sub)
+                for (int sub = 0; sub < NGRP; ++sub)
 #pragma unroll
                     for (int m = 0; m < M; ++m) {
                         float pv = 0.0f;
@@ -814,7 +924,7 @@ __global__ void __launch_bounds__(ts_threads(NSUB, M), 1)
                 ts_bar_arrive(1 + 2 * w + buf, 160);   // releases the issuer; also: the stage of step i has been read
             }
 #pragma unroll
-            for (int sub = 0; sub < NSUB; ++sub)
+            for (int sub = 0; sub < NGRP; ++sub)
 #pragma unroll
                 for (int m = 0; m < M; ++m) {
                     s2[sub][m] = s1[sub][m];
@@ -839,32 +949,35 @@ __global__ void __launch_bounds__(ts_threads(NSUB, M), 1)
 // host
 // ---------------------------------------------------------------------------------------------
 struct TsPlan {
-    int KB, NT, grid, cache_in_smem, stages, smem;
+    int KB, NT, KS, grid, cache_in_smem, stages, smem;
     int off_red, off_cache, off_ring, off_b;
-    int xq_bytes;
-    size_t partial_bytes;
+    int steps_bytes, xq_bytes;
 };
+
+// Two 256-k blocks per step where the kernel has that form: one activation row, one group per block, an even number of blocks.
+static int ts_choose_ks(const PackedW& w, int M) { return (M == 1 && w.G == 256 && (w.K / 256) % 2 == 0) ? 2 : 1; }
 
 static int ts_plan(const PackedW& w, int M, const DeviceInfo& di, TsPlan* pl) {
     const int NSUB = 256 / w.G, TN = ts_tn(w.S);
-    const int NWG = ts_nwg(NSUB, M);
+    const int KS = ts_choose_ks(w, M);
+    const int NWG = ts_nwg(NSUB, M, KS);
+    pl->KS = KS;
     pl->KB = w.K / 256;
     pl->NT = w.N / TN;
-    const long long T = (long long)pl->NT * pl->KB;
     // Up to one row tile per SM: a CTA owns whole tiles and nothing is exchanged between CTAs (measured: the exchange at the
     // end of a CTA that owns no whole tile costs 2.5-4.5 us).  More tiles than SMs: every SM takes the same number of
     // steps; tiles that straddle CTAs are exchanged early, behind the whole tiles' work.
     pl->grid = pl->NT <= di.sm_count ? pl->NT : di.sm_count;
-    pl->xq_bytes = ts_round_up(pl->KB * M * 1024 + M * pl->KB * NSUB * 4, 16);
-    pl->partial_bytes = (size_t)pl->grid * 2 * M * TN * sizeof(float);
+    pl->steps_bytes = ts_round_up(M * pl->KB * NSUB * 4, 16);
+    pl->xq_bytes = pl->KB * M * 1024 + pl->steps_bytes;
     const int red_bytes = 2 * NWG * M * 128 * 4;
     const int cache_bytes = w.idx_bytes ? ts_round_up(w.C * w.S * 2, 16) : 0;
-    const int bbytes = pl->xq_bytes + TS_BSLACK;
+    const int bbytes = 1024 + pl->KB * M * 1024 + 1024 + pl->steps_bytes + TS_BSLACK;     // zeros, digits, zeros, steps, slack
     auto layout = [&](int cb, int stages) {
         pl->off_red = TS_HDR;
         pl->off_cache = pl->off_red + red_bytes;
         pl->off_ring = ts_round_up(pl->off_cache + cb, 128);
-        pl->off_b = ts_round_up(pl->off_ring + NWG * stages * TS_STAGE_BYTES, 1024);
+        pl->off_b = ts_round_up(pl->off_ring + NWG * stages * ts_stage_bytes(KS), 1024);
         return pl->off_b + bbytes;
     };
     // the codebook goes to shared memory if at least four stages per warpgroup still fit next to it
@@ -887,34 +1000,33 @@ bool linear_tcs_supported(const PackedW& w, int M) {
     if (reinterpret_cast<uintptr_t>(w.coeff) & 15) return false;                 // bulk copies
     if (reinterpret_cast<uintptr_t>(w.bvr) & 15) return false;                   // tensor map base
     if (w.idx_bytes && (reinterpret_cast<uintptr_t>(w.idx) & 15)) return false;
-    if (w.N / ts_tn(w.S) > SBVR_WS_COUNTERS) return false;                       // one arrival counter per row tile
     if ((size_t)(w.N / ts_tn(w.S)) * (size_t)(w.K / 256) >= ((size_t)1 << 24)) return false;   // 32-bit step arithmetic (steps x CTAs)
     if ((size_t)w.N * w.S >= ((size_t)1 << 31)) return false;                    // 32-bit tensor coordinates
     // the activation digits of the whole K stay resident in shared memory: K/256 * M KB, beside two stages at least
-    const int NSUB = 256 / w.G, KB = w.K / 256, NWG = ts_nwg(NSUB, M);
-    const int xq = ts_round_up(KB * M * 1024 + M * KB * NSUB * 4, 16);
-    const int need = ts_round_up(ts_round_up(TS_HDR + 2 * NWG * M * 128 * 4, 128) + NWG * 2 * TS_STAGE_BYTES, 1024) + xq +
-                     TS_BSLACK;
+    const int NSUB = 256 / w.G, KB = w.K / 256, KS = ts_choose_ks(w, M), NWG = ts_nwg(NSUB, M, KS);
+    const int need = ts_round_up(ts_round_up(TS_HDR + 2 * NWG * M * 128 * 4, 128) + NWG * 2 * ts_stage_bytes(KS), 1024) + 2048 +
+                     KB * M * 1024 + ts_round_up(M * KB * NSUB * 4, 16) + TS_BSLACK;
     return need <= 227 * 1024;
 }
 
 size_t linear_tcs_workspace_bytes(const PackedW& w, int M, int sm_count) {
-    const int NSUB = 256 / w.G, TN = ts_tn(w.S), KB = w.K / 256;
-    const size_t xq = (size_t)ts_round_up(KB * M * 1024 + M * KB * NSUB * 4, 16);
-    return ((xq + 255) / 256) * 256 + (size_t)sm_count * 2 * M * TN * sizeof(float);
+    (void)sm_count;
+    const int NSUB = 256 / w.G, KB = w.K / 256;
+    const size_t xq = (size_t)KB * M * 1024 + (size_t)ts_round_up(M * KB * NSUB * 4, 16);
+    return ((xq + 255) / 256) * 256;
 }
 
-// ---- tensor maps of the packed words: uint32 [K/32 rows][N * S], box 8 rows x TN * S words
+// ---- tensor maps of the packed words: uint32 [K/32 rows][N * S], box 8 KS rows x TN * S words
 typedef CUresult (*TsEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-static int ts_tensor_map(const PackedW& w, CUtensorMap* out) {
+static int ts_tensor_map(const PackedW& w, int KS, CUtensorMap* out) {
     static std::mutex mu;
     static TsEncodeFn encode = nullptr;
     struct Entry {
         const void* bvr;
-        int N, K, S, valid;
+        int N, K, S, KS, valid;
         CUtensorMap map;
     };
     static Entry cache[64];
@@ -928,10 +1040,10 @@ static int ts_tensor_map(const PackedW& w, CUtensorMap* out) {
     }
     const size_t h = (reinterpret_cast<uintptr_t>(w.bvr) >> 8) * 0x9E3779B97F4A7C15ull;
     Entry& e = cache[(h >> 40) & 63];
-    if (!(e.valid && e.bvr == w.bvr && e.N == w.N && e.K == w.K && e.S == w.S)) {
+    if (!(e.valid && e.bvr == w.bvr && e.N == w.N && e.K == w.K && e.S == w.S && e.KS == KS)) {
         const cuuint64_t dims[2] = {(cuuint64_t)w.N * w.S, (cuuint64_t)w.K / 32};
         const cuuint64_t strides[1] = {(cuuint64_t)w.N * w.S * 4};
-        const cuuint32_t box[2] = {(cuuint32_t)(ts_tn(w.S) * w.S), 8u};
+        const cuuint32_t box[2] = {(cuuint32_t)(ts_tn(w.S) * w.S), (cuuint32_t)(8 * KS)};
         const cuuint32_t estr[2] = {1u, 1u};
         const CUresult r = encode(&e.map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint32_t*>(w.bvr), dims, strides, box,
                                   estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
@@ -941,51 +1053,63 @@ static int ts_tensor_map(const PackedW& w, CUtensorMap* out) {
             g_last_cuda_error = (int)r;
             return SBVR_ERR_CUDA;
         }
-        e.bvr = w.bvr, e.N = w.N, e.K = w.K, e.S = w.S, e.valid = 1;
+        e.bvr = w.bvr, e.N = w.N, e.K = w.K, e.S = w.S, e.KS = KS, e.valid = 1;
     }
     *out = e.map;
     return SBVR_OK;
 }
 
-template <int S, int NSUB, int M, int IDXB>
+template <int S, int NSUB, int M, int IDXB, int KS>
 static int ts_launch_inst(const CUtensorMap& tm, const TsParams& p, int grid, int smem, cudaStream_t st) {
     static SmemOnce once;
-    const int rc = set_max_smem_once(once, linear_tcs_kernel<S, NSUB, M, IDXB>, 227 * 1024);
+    const int rc = set_max_smem_once(once, linear_tcs_kernel<S, NSUB, M, IDXB, KS>, 227 * 1024);
     if (rc) return rc;
-    SBVR_CUDA_TRY(launch_pdl(linear_tcs_kernel<S, NSUB, M, IDXB>, dim3(grid), dim3(ts_threads(NSUB, M)), (size_t)smem, st, tm,
-                             p));
+    SBVR_CUDA_TRY(launch_pdl(linear_tcs_kernel<S, NSUB, M, IDXB, KS>, dim3(grid), dim3(ts_threads(NSUB, M, KS)), (size_t)smem,
+                             st, tm, p));
     return SBVR_OK;
 }
 template <int S, int NSUB, int M>
-static int ts_launch_idx(const CUtensorMap& tm, const TsParams& p, int idxb, int grid, int smem, cudaStream_t st) {
+static int ts_launch_idx(const CUtensorMap& tm, const TsParams& p, int idxb, int KS, int grid, int smem, cudaStream_t st) {
+    if constexpr (NSUB == 1 && M == 1) {
+        if (KS == 2) {
+            switch (idxb) {
+                case 0: return ts_launch_inst<S, NSUB, M, 0, 2>(tm, p, grid, smem, st);
+                case 1: return ts_launch_inst<S, NSUB, M, 1, 2>(tm, p, grid, smem, st);
+                default: return ts_launch_inst<S, NSUB, M, 2, 2>(tm, p, grid, smem, st);
+            }
+        }
+    }
     switch (idxb) {
-        case 0: return ts_launch_inst<S, NSUB, M, 0>(tm, p, grid, smem, st);
-        case 1: return ts_launch_inst<S, NSUB, M, 1>(tm, p, grid, smem, st);
-        default: return ts_launch_inst<S, NSUB, M, 2>(tm, p, grid, smem, st);
+        case 0: return ts_launch_inst<S, NSUB, M, 0, 1>(tm, p, grid, smem, st);
+        case 1: return ts_launch_inst<S, NSUB, M, 1, 1>(tm, p, grid, smem, st);
+        default: return ts_launch_inst<S, NSUB, M, 2, 1>(tm, p, grid, smem, st);
     }
 }
 template <int S, int NSUB>
-static int ts_launch_m(const CUtensorMap& tm, const TsParams& p, int M, int idxb, int grid, int smem, cudaStream_t st) {
+static int ts_launch_m(const CUtensorMap& tm, const TsParams& p, int M, int idxb, int KS, int grid, int smem,
+                       cudaStream_t st) {
     switch (M) {
-        case 1: return ts_launch_idx<S, NSUB, 1>(tm, p, idxb, grid, smem, st);
-        case 2: return ts_launch_idx<S, NSUB, 2>(tm, p, idxb, grid, smem, st);
-        case 3: return ts_launch_idx<S, NSUB, 3>(tm, p, idxb, grid, smem, st);
-        default: return ts_launch_idx<S, NSUB, 4>(tm, p, idxb, grid, smem, st);
+        case 1: return ts_launch_idx<S, NSUB, 1>(tm, p, idxb, KS, grid, smem, st);
+        case 2: return ts_launch_idx<S, NSUB, 2>(tm, p, idxb, KS, grid, smem, st);
+        case 3: return ts_launch_idx<S, NSUB, 3>(tm, p, idxb, KS, grid, smem, st);
+        default: return ts_launch_idx<S, NSUB, 4>(tm, p, idxb, KS, grid, smem, st);
     }
 }
 template <int S>
-static int ts_launch_g(const CUtensorMap& tm, const TsParams& p, int G, int M, int idxb, int grid, int smem,
+static int ts_launch_g(const CUtensorMap& tm, const TsParams& p, int G, int M, int idxb, int KS, int grid, int smem,
                        cudaStream_t st) {
-    return G == 256 ? ts_launch_m<S, 1>(tm, p, M, idxb, grid, smem, st) : ts_launch_m<S, 2>(tm, p, M, idxb, grid, smem, st);
+    return G == 256 ? ts_launch_m<S, 1>(tm, p, M, idxb, KS, grid, smem, st)
+                    : ts_launch_m<S, 2>(tm, p, M, idxb, KS, grid, smem, st);
 }
 
-// `scratch` (256-byte aligned, linear_tcs_workspace_bytes long), `status` and `counters` (one zeroed word per row
-// tile) are the caller's: the workspace form and the no-allocation form carve them differently.
+// `scratch` (256-byte aligned, linear_tcs_workspace_bytes long), `status` and `xchg` (SBVR_WS_XCHG_BYTES of exchange slots,
+// all zero between calls: the kernel leaves them zero) are the caller's: the workspace form and the no-allocation form
+// carve them differently.
 int launch_linear_tcs(const __half* x, const PackedW& w, const __half* bias, __half* y, int M, int device,
-                      unsigned int* status, unsigned int* counters, char* scratch, size_t scratch_bytes, cudaStream_t st,
+                      unsigned int* status, unsigned long long* xchg, char* scratch, size_t scratch_bytes, cudaStream_t st,
                       const XOp* xop) {
     if (!linear_tcs_supported(w, M)) return SBVR_ERR_UNSUPPORTED;
-    if (!status || !counters || !scratch) return SBVR_ERR_WORKSPACE;
+    if (!status || !xchg || !scratch) return SBVR_ERR_WORKSPACE;
     if (reinterpret_cast<uintptr_t>(x) & 15) return SBVR_ERR_ALIGN;      // x is fetched 16 bytes at a time
     if (reinterpret_cast<uintptr_t>(scratch) & 255) return SBVR_ERR_ALIGN;
     DeviceInfo di;
@@ -996,6 +1120,7 @@ int launch_linear_tcs(const __half* x, const PackedW& w, const __half* bias, __h
     rc = ts_plan(w, M, di, &pl);
     if (rc) return rc;
     if (linear_tcs_workspace_bytes(w, M, di.sm_count) > scratch_bytes) return SBVR_ERR_WORKSPACE;
+    if ((size_t)pl.grid * 2 * M * ts_tn(w.S) * 8 > SBVR_WS_XCHG_BYTES) return SBVR_ERR_UNSUPPORTED;
     XqParams xp;
     xp.x = x, xp.xq = reinterpret_cast<unsigned char*>(scratch), xp.K = w.K, xp.KB = pl.KB, xp.M = M;
     xp.x_op = xop ? xop->op : SBVR_XOP_NONE;
@@ -1017,12 +1142,12 @@ int launch_linear_tcs(const __half* x, const PackedW& w, const __half* bias, __h
             return SBVR_ERR_ALIGN;
     }
     CUtensorMap tm;
-    rc = ts_tensor_map(w, &tm);
+    rc = ts_tensor_map(w, pl.KS, &tm);
     if (rc) return rc;
     // one block per compute warp at most: the CTAs quantise for themselves; longer rows (and rows with an op in front)
     // get the separate kernel
-    const int NWG = ts_nwg(256 / w.G, M);
-    const bool in_kernel = (xp.x_op == SBVR_XOP_NONE) && (M * pl.KB <= NWG * 4);
+    const int NWG = ts_nwg(256 / w.G, M, pl.KS);
+    const bool in_kernel = (xp.x_op == SBVR_XOP_NONE) && (M * pl.KB <= ts_cw0(256 / w.G, M, pl.KS) + 4 * NWG);
     if (!in_kernel) {
         const dim3 qgrid((pl.KB + 15) / 16, M);
         if (w.G == 256) SBVR_CUDA_TRY(launch_pdl(xquant_kernel<1>, qgrid, dim3(512), 0, st, xp));
@@ -1031,15 +1156,14 @@ int launch_linear_tcs(const __half* x, const PackedW& w, const __half* bias, __h
     TsParams p;
     p.x = x, p.x_in_kernel = in_kernel ? 1 : 0;
     p.xq = xp.xq, p.idx = w.idx, p.coeff = w.coeff, p.bias = bias, p.y = y;
-    p.status = status, p.counters = counters;
-    p.partials = reinterpret_cast<float*>(scratch + ((size_t)pl.xq_bytes + 255) / 256 * 256);
+    p.status = status, p.xchg = xchg;
     p.N = w.N, p.K = w.K, p.KB = pl.KB, p.NT = pl.NT, p.C = w.C, p.cache_in_smem = pl.cache_in_smem, p.stages = pl.stages;
-    p.xq_bytes = pl.xq_bytes;
+    p.steps_bytes = pl.steps_bytes;
     p.off_red = pl.off_red, p.off_cache = pl.off_cache, p.off_ring = pl.off_ring, p.off_b = pl.off_b;
     switch (w.S) {
-        case 2: return ts_launch_g<2>(tm, p, w.G, M, w.idx_bytes, pl.grid, pl.smem, st);
-        case 3: return ts_launch_g<3>(tm, p, w.G, M, w.idx_bytes, pl.grid, pl.smem, st);
-        default: return ts_launch_g<4>(tm, p, w.G, M, w.idx_bytes, pl.grid, pl.smem, st);
+        case 2: return ts_launch_g<2>(tm, p, w.G, M, w.idx_bytes, pl.KS, pl.grid, pl.smem, st);
+        case 3: return ts_launch_g<3>(tm, p, w.G, M, w.idx_bytes, pl.KS, pl.grid, pl.smem, st);
+        default: return ts_launch_g<4>(tm, p, w.G, M, w.idx_bytes, pl.KS, pl.grid, pl.smem, st);
     }
 }
 

@@ -97,13 +97,14 @@ extern "C" int sbvr_linear_f16_noalloc(const void* x, const uint32_t* bvr, const
     rc = device_info(dev, &di);
     if (rc) return rc;
     // carve the static array exactly like an allocated workspace
-    const size_t fixed = 256 + (size_t)SBVR_WS_COUNTERS * 4;
+    const size_t fixed = SBVR_WS_FIXED_BYTES;
     sbvr_workspace ws;
     ws.device = dev;
     ws.bytes = SBVR_NOALLOC_BYTES;
     ws.base = reinterpret_cast<char*>(base);
     ws.status = reinterpret_cast<unsigned int*>(ws.base);
     ws.counters = reinterpret_cast<unsigned int*>(ws.base + 256);
+    ws.xchg = reinterpret_cast<unsigned long long*>(ws.base + 256 + (size_t)SBVR_WS_COUNTERS * 4);
     ws.dyn = ws.base + fixed;
     ws.dyn_bytes = SBVR_NOALLOC_BYTES - fixed;
     ws.pinned_status = nullptr;
@@ -123,7 +124,7 @@ extern "C" int sbvr_linear_f16_noalloc(const void* x, const uint32_t* bvr, const
     // whatever the previous call (possibly an aborted one) left in the status word and the counters must go
     SBVR_CUDA_TRY(cudaMemsetAsync(ws.base, 0, fixed, st));
     if (kind == 1)
-        rc = launch_linear_tcs(xh, w, bh, yh, M, dev, ws.status, ws.counters, ws.dyn, ws.dyn_bytes, st);
+        rc = launch_linear_tcs(xh, w, bh, yh, M, dev, ws.status, ws.xchg, ws.dyn, ws.dyn_bytes, st);
     else
         rc = launch_linear_gemm(xh, w, bh, yh, M, &ws, st);
     if (rc == SBVR_ERR_WORKSPACE) return SBVR_ERR_NOALLOC_LIMIT;
