@@ -75,6 +75,7 @@ struct TsParams {
     unsigned int* status;
     unsigned long long* xchg;     // [grid][2][M * TN] (fp32 sum | tag << 32) of the shared segments; all zero between calls
     int N, K, KB, NT, C, cache_in_smem, stages;
+    int pre_stages;               // stages requested before the activations are fetched
     int steps_bytes;              // bytes of the steps, rounded up to a multiple of 16
     int off_red, off_cache, off_ring, off_b;      // shared-memory carve-up; at off_b: [1 KB zeros][digits][1 KB zeros][steps]
 };
@@ -452,7 +453,9 @@ __global__ void __launch_bounds__(ts_threads(NSUB, M, KS), 1)
     // rows are quantised here, by every CTA for itself, one 256-k block per warp: cheaper than a launch of its own in
     // front of this one (a kernel boundary costs more than the ~1 us this takes).  Only the k blocks this CTA's steps
     // touch are done.  Either way the warp then reports on b_ready (its generic writes made visible to the MMA's reads).
-    auto digits_share = [&]() {
+    // `after_fetch` runs once this warp's activations have arrived (the issuers request the rest of their first stages
+    // there: requested earlier, those 100+ KB per SM queue in front of the activations and delay them by over a microsecond).
+    auto digits_share = [&](auto after_fetch) {
         if (warp == CW0) {                         // the two zero blocks beside the digits
             reinterpret_cast<uint4*>(Z0)[lane] = make_uint4(0u, 0u, 0u, 0u);
             reinterpret_cast<uint4*>(Z0)[lane + 32] = make_uint4(0u, 0u, 0u, 0u);
@@ -467,14 +470,18 @@ __global__ void __launch_bounds__(ts_threads(NSUB, M, KS), 1)
                 kb_lo = sg.k0(0) * KS;
                 nkb = (sg.k1(0) - sg.k0(0)) * KS;
             }
-            for (int blk = warp; blk < M * nkb; blk += NWARPS) {
-                const int m = blk / nkb, kb = kb_lo + (blk - m * nkb);
-                unsigned char* area = Bs + ((size_t)kb * M + m) * 1024;
+            const int blk = warp;                  // M * nkb <= NWARPS: at most one block per warp
+            const bool mine = blk < M * nkb;
+            const int m = mine ? blk / nkb : 0, kb = mine ? kb_lo + (blk - m * nkb) : 0;
+            unsigned char* area = Bs + ((size_t)kb * M + m) * 1024;
+            if (mine)
                 reinterpret_cast<uint4*>(area)[lane] =
                     __ldg(reinterpret_cast<const uint4*>(p.x + (size_t)m * p.K + (size_t)kb * 256) + lane);
-                __syncwarp();
-                xdigits_block<NSUB>(area, xsc + ((size_t)m * KB + kb) * NSUB, lane);
-            }
+            __syncwarp();
+            after_fetch();
+            if (mine) xdigits_block<NSUB>(area, xsc + ((size_t)m * KB + kb) * NSUB, lane);
+        } else {
+            after_fetch();
         }
         fence_proxy_async();
         __syncwarp();
@@ -495,7 +502,7 @@ __global__ void __launch_bounds__(ts_threads(NSUB, M, KS), 1)
         __syncwarp();
         if (lane == 0) mbar_arrive(tmem_ready);    // whoever needs tensor memory waits for this
         pdl_wait();                                // digits, scratch and y belong to the stream's earlier kernels until now
-        digits_share();
+        digits_share([] {});
         if (lane == 0 && !p.x_in_kernel) {
             const uint32_t dig = (uint32_t)(KB * M * 1024);
             mbar_arrive_expect_tx(b_ready, dig + (uint32_t)p.steps_bytes);
@@ -671,11 +678,15 @@ __global__ void __launch_bounds__(ts_threads(NSUB, M, KS), 1)
         };
         // weights do not depend on the previous kernel of the stream: the first stages are requested at once
         {
-            const int first = n_w < ST ? n_w : ST;
+            const int first = n_w < p.pre_stages ? n_w : p.pre_stages;
 #pragma unroll 1
             for (int i = 0; i < first; ++i) load_step();
         }
-        digits_share();
+        digits_share([&] {
+            const int first = n_w < ST ? n_w : ST;
+#pragma unroll 1
+            while (issued < first) load_step();
+        });
         ts_wait(smem_u32(tmem_ready), 0u, abort_flag, p.status, 0x312u);                  // tensor memory is allocated
         ts_wait(smem_u32(sf_ready), 0u, abort_flag, p.status, 0x313u);                    // ... and holds the scale factors
         ts_fence_after();
@@ -737,7 +748,7 @@ __global__ void __launch_bounds__(ts_threads(NSUB, M, KS), 1)
         }
     } else if (warp < CW0) {
         // ------------------------------ spare warps: their share of the digits, then nothing until the teardown ----
-        digits_share();
+        digits_share([] {});
     } else {
         // ------------------------------ compute warpgroups ------------------------------
         const int w = (warp - CW0) >> 2, wl = warp & 3;
@@ -768,7 +779,7 @@ __global__ void __launch_bounds__(ts_threads(NSUB, M, KS), 1)
             if (lane == 0) mbar_arrive(sf_ready);  // the issuers wait for the four warps
         }
         if (p.cache_in_smem && !bulk_cache) named_bar_sync(15, NWG * 128);                // the hand-copied codebook is complete
-        digits_share();
+        digits_share([] {});
         if (bulk_cache) ts_wait(smem_u32(cache_bar), 0u, abort_flag, p.status, 0x320u);
         ts_wait(smem_u32(b_ready), 0u, abort_flag, p.status, 0x321u);                      // digits and steps are in place
 
@@ -1159,6 +1170,7 @@ int launch_linear_tcs(const __half* x, const PackedW& w, const __half* bias, __h
     p.status = status, p.xchg = xchg;
     p.N = w.N, p.K = w.K, p.KB = pl.KB, p.NT = pl.NT, p.C = w.C, p.cache_in_smem = pl.cache_in_smem, p.stages = pl.stages;
     p.steps_bytes = pl.steps_bytes;
+    p.pre_stages = pl.stages < 3 ? pl.stages : 3;
     p.off_red = pl.off_red, p.off_cache = pl.off_cache, p.off_ring = pl.off_ring, p.off_b = pl.off_b;
     switch (w.S) {
         case 2: return ts_launch_g<2>(tm, p, w.G, M, w.idx_bytes, pl.KS, pl.grid, pl.smem, st);

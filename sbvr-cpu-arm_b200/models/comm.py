@@ -16,7 +16,11 @@ class SymmetricAllReduce:
     FLAG_BYTES = 1024
 
     def __init__(self, group, device, max_rows: int, hidden: int, calls_per_step: int):
+        import os
         import torch.distributed as dist
+        # the all-reduce kernel reads the peers with plain loads: the allocator need not (and, so that a rank that dies
+        # does not leave peers bound to an NVLink multicast object, should not) create a multicast mapping
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm
         self.group = group
         self.world = dist.get_world_size(group)

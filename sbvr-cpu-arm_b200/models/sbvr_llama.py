@@ -59,6 +59,10 @@ class LlamaConfig:
             return LlamaConfig(hidden_size=512, intermediate_size=1024, num_hidden_layers=2, num_attention_heads=4,
                                num_key_value_heads=2, vocab_size=1024, codebook_lines=256,
                                max_position_embeddings=512)
+        if name == "tiny8":                        # eight KV heads: splits over up to eight tensor-parallel ranks
+            return LlamaConfig(hidden_size=1024, intermediate_size=2048, num_hidden_layers=2, num_attention_heads=8,
+                               num_key_value_heads=8, vocab_size=1024, codebook_lines=256,
+                               max_position_embeddings=512)
         raise ValueError(f"unknown preset {name}")
 
 

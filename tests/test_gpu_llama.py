@@ -239,3 +239,62 @@ def test_rope_attention_equals_rope_then_attention(ctx, nsplit):
                                                     d ** -0.5, nsplit, st))
     assert torch.equal(K1, K2) and torch.equal(V1, V2)
     assert torch.equal(o1, o2)
+
+
+def test_llama3_8b_architecture_two_layers_logits_and_greedy_agreement(capsys):
+    """Two decoder layers with the Llama-3-8B dimensions (hidden 4096, 32 heads, 8 KV heads, intermediate 14336, theta 5e5;
+    the vocabulary is cut to 8192 rows to keep the CPU decode of the head short) against the restated reference model:
+    prompt logits, 256 teacher-forced decode steps over the KV cache, and a free-running greedy comparison whose first
+    divergence (if any) must be a near-tie of the reference's own logits."""
+    from models.sbvr_llama import LlamaConfig, SBVRLlamaForCausalLM
+    cfg = LlamaConfig.preset("8b")
+    cfg.num_hidden_layers = 2
+    cfg.vocab_size = 8192
+    steps, prompt = 256, 32
+    m = SBVRLlamaForCausalLM(cfg, max_batch=1, max_ctx=prompt + steps + 8).init_synthetic(11)
+    params = _ref_params(m)
+    gen = torch.Generator(device="cuda").manual_seed(21)
+    ids = torch.randint(0, cfg.vocab_size, (1, prompt), device="cuda", generator=gen)
+
+    # prompt logits
+    logits = m(ids).float()
+    ref = llama_ref.forward(params, ids).float()
+    err = ((logits - ref).abs().max() / ref.abs().max()).item()
+    assert err <= TOL, err
+
+    # the reference's own greedy continuation (full causal forward every step)
+    seq = ids.clone()
+    ref_step_logits = []
+    for _ in range(steps):
+        lg = llama_ref.forward(params, seq)[:, -1].float()
+        ref_step_logits.append(lg)
+        seq = torch.cat((seq, lg.argmax(-1, keepdim=True)), dim=1)
+    ref_tokens = seq[:, prompt:]                                    # [1, steps]
+
+    # teacher-forced: our decode steps fed with the reference's tokens
+    first = m.prefill(ids)
+    agree = [bool((first.long() == ref_tokens[:, 0]).all())]
+    worst = 0.0
+    for t in range(steps - 1):
+        pos = torch.full((1,), prompt + t, dtype=torch.int32, device="cuda")
+        nxt = m.decode_step(ref_tokens[:, t].to(torch.int32), pos)
+        lg = m._act(1, 1).logits.float()
+        r = ref_step_logits[t + 1]
+        worst = max(worst, ((lg - r).abs().max() / r.abs().max()).item())
+        agree.append(bool((nxt.long() == ref_tokens[:, t + 1]).all()))
+    assert worst <= TOL, worst
+    frac = sum(agree) / len(agree)
+    assert frac >= 0.97, frac
+
+    # free-running greedy (CUDA graph): the first divergence, if any, is a near-tie in the reference
+    ours = m.generate(ids, steps, use_graph=True)
+    diff = (ours.long() != ref_tokens).nonzero()
+    first_div = int(diff[0, 1]) if diff.numel() else None
+    if first_div is not None:
+        r = ref_step_logits[first_div][0]
+        gap = (r.max() - r[ours[0, first_div].long()]).item()
+        assert gap <= 2e-2 * r.abs().max().item(), (first_div, gap)
+    with capsys.disabled():
+        print(f"\n[8B-architecture, 2 layers] prompt logits err {err:.2e}; teacher-forced: worst step err {worst:.2e}, "
+              f"token agreement {frac:.4f} over {steps} steps; free-running greedy first divergence: {first_div}")
+    m._check()

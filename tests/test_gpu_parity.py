@@ -397,3 +397,60 @@ def test_row_deq_mm_T_llama_shapes_deterministic(shape):
     assert ((y.double() - ref).abs().max() / ref.abs().max()).item() <= 2e-3
     assert torch.equal(y, sbvr.row_deq_mm_T(x, w_t))
     check_status()
+
+
+@pytest.mark.parametrize("shape", [(14336, 4096), (4096, 14336)])
+def test_prefill_gemm_m2048_llama_shapes(shape):
+    """The prefill configuration itself: M = 2048 tokens on the gate/up and down shapes, against the dense fp32 product of
+    the decoded weight (the CPU oracle decodes, the comparison product runs on the GPU in fp32)."""
+    import sbvr
+    N, K = shape
+    p = O.make_packed(N, K, 4, G=256, mode="u16", C=4096, seed=N % 89)
+    w = to_sbvr(p)
+    g = torch.Generator(device="cuda").manual_seed(K)
+    x = torch.randn((2048, K), device="cuda", generator=g).half()
+    Wd = torch.from_numpy(O.decode_c(p["bvr"], p["coeff_idx"], p["coeff"], G=256)).cuda()
+    ref = (x.float() @ Wd.float().T)
+    y = sbvr.linear(x, w, None).float()
+    err = ((y - ref).abs().max() / ref.abs().max()).item()
+    assert err <= TOL, err
+    assert err <= 3e-3, err
+    check_status()
+
+
+@pytest.mark.parametrize("shape", [(4096, 4096), (1024, 4096), (14336, 4096), (4096, 14336)])
+@pytest.mark.parametrize("M", [1, 4, 16])
+def test_group128_direct_llama_shapes(shape, M):
+    """Group length 128 with one coefficient line per (group, row) (no codebook: 128 k groups x 14336 rows exceed 65536
+    lines) on the four Llama-3-8B shapes."""
+    import sbvr
+    N, K = shape
+    p = O.make_packed(N, K, 4, G=128, mode="direct", seed=N % 83 + M)
+    w = to_sbvr(p)
+    rng = np.random.default_rng(M + K)
+    x = rng.standard_normal((M, K)).astype(np.float16)
+    ref = O.linear_c(x, p["bvr"], p["coeff_idx"], p["coeff"], G=128)
+    y = h2n(sbvr.linear(torch.from_numpy(x).cuda(), w, None))
+    err = O.max_rel_err(y, ref)
+    assert err <= TOL, err
+    assert err <= 3e-3, err
+    check_status()
+
+
+@pytest.mark.parametrize("shape", [(4096, 4096), (1024, 4096), (14336, 4096), (4096, 14336)])
+@pytest.mark.parametrize("M", [16, 32])
+@pytest.mark.parametrize("S", [2, 3, 4])
+def test_small_batches_llama_shapes(shape, M, S):
+    """The small-batch corners of the sweep configuration: M in {16, 32} x bit-plane counts {2, 3, 4} on every layer shape."""
+    import sbvr
+    N, K = shape
+    p = O.make_packed(N, K, S, G=256, mode="u16", C=4096, seed=S * 7 + M)
+    w = to_sbvr(p)
+    rng = np.random.default_rng(M * S)
+    x = rng.standard_normal((M, K)).astype(np.float16)
+    ref = O.linear_c(x, p["bvr"], p["coeff_idx"], p["coeff"], G=256)
+    y = h2n(sbvr.linear(torch.from_numpy(x).cuda(), w, None))
+    err = O.max_rel_err(y, ref)
+    assert err <= TOL, err
+    assert err <= 3e-3, err
+    check_status()
