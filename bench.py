@@ -13,7 +13,10 @@ cycled, so every step streams weights that left L2 (126 MB) long ago.
 metric `sbvr_gemv_hbm_gbs_m1` = algorithmic bytes of a step (planes + indices + codebook + x + y,
 111.1 MB) / time of a step, summed over GPUs.  With N > 1 every rank runs the same per-GPU work on
 its own weights (output-row shards of an N-times larger layer stack): no data-path collective,
-weak scaling; time = max over ranks.
+weak scaling; time = max over ranks.  The timed region (--steps steps) is repeated 11 times and the
+median is reported.  At N > 1 the line also carries `strong_rows` (ONE layer's rows split over the
+ranks) and `tp_parity` (tensor-parallel logits against one rank), and the Llama decode sections run
+tensor parallel over all ranks.
 
 One JSON line is printed by rank 0.
 """
@@ -33,8 +36,9 @@ SHAPES = [("q", 4096, 4096), ("k", 1024, 4096), ("v", 1024, 4096), ("o", 4096, 4
           ("gate", 14336, 4096), ("up", 14336, 4096), ("down", 4096, 14336)]
 S, G, C, IDXB = 4, 256, 4096, 2
 N_LAYERS = 4
-# dram__bytes_read.sum + dram__bytes_write.sum of one linear_tc_kernel launch at 14336x4096 (ncu, see profiles/)
-TRAFFIC_DOMINANT = 29_910_784
+REPEATS = 11                  # repeats of every timed region; the median is reported, min and max beside it
+# dram__bytes_read.sum + dram__bytes_write.sum of one linear_tcs_kernel launch at 14336x4096 (ncu, see profiles/)
+TRAFFIC_DOMINANT = 29_920_000
 
 
 def alg_bytes(M, N, K, s=S, g=G, ib=IDXB, c=C):
@@ -150,20 +154,29 @@ def run_ours(args):
         sampler = ClockSampler(local)
         if rank == 0:
             sampler.start()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        for i in range(args.steps):
-            graphs[i % N_LAYERS].replay()
-        e1.record(stream)
-        e1.synchronize()
-        torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1)
+        # the timed region (exactly --steps steps between two events) is repeated; the median repeat is reported
+        rep_ms = []
+        for rep in range(REPEATS):
+            if dist:
+                dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for i in range(args.steps):
+                graphs[i % N_LAYERS].replay()
+            e1.record(stream)
+            e1.synchronize()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1)
+            if dist:
+                t = torch.tensor([ms], device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                ms = float(t.item())
+            rep_ms.append(ms)
         if dist:
-            t = torch.tensor([ms], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
             dist.barrier()
         clocks = sampler.stop() if rank == 0 else None
+        ms = sorted(rep_ms)[len(rep_ms) // 2]
 
         # ---- the dominant kernel alone (gate/up shape): one launch per linear
         Nd, Kd = 14336, 4096
@@ -185,12 +198,15 @@ def run_ours(args):
                 dom(i)
         gd.replay()
         torch.cuda.synchronize()
-        d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        d0.record(stream)
-        gd.replay()
-        d1.record(stream)
-        d1.synchronize()
-        dom_us = d0.elapsed_time(d1) * 1e3 / reps
+        dom_all = []
+        for _ in range(REPEATS):
+            d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            d0.record(stream)
+            gd.replay()
+            d1.record(stream)
+            d1.synchronize()
+            dom_all.append(d0.elapsed_time(d1) * 1e3 / reps)
+        dom_us = sorted(dom_all)[len(dom_all) // 2]
 
         # ---- end to end through the public API with host buffers (copies inside the timed region)
         # the step's activations (hidden-sized and intermediate-sized row) sit in one pinned host buffer, its seven results
@@ -241,6 +257,9 @@ def run_ours(args):
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             e2e_s = float(t.item())
     extra = {}
+    if world > 1:
+        extra["strong_rows"] = strong_rows(torch, dev, dist, world, stream, gen)
+        extra["tp_parity"] = tp_parity(torch, dev, dist, world)
     if not args.no_extras:
         if world == 1:
             extra.update(small_m_and_prefill(torch, dev, stream))
@@ -266,21 +285,26 @@ def run_ours(args):
     line = {
         "metric": "sbvr_gemv_hbm_gbs_m1", "value": round(value, 1), "unit": "GB/s", "n_gpus": world,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 5),
+        "repeats": {"n": REPEATS, "statistic": "median", "ms_per_step_min": round(min(rep_ms) / args.steps, 5),
+                    "ms_per_step_max": round(max(rep_ms) / args.steps, 5)},
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
         "config": {"workload": "llama3-8b decoder-layer linears (q,k,v,o,gate,up,down), M=1, S=4, G=256, "
                                "u16 codebook C=4096", "bytes_per_step": STEP_BYTES,
                    "l2": "inputs larger than L2: 4 layers = 444 MB of packed weights cycled",
-                   "launch": "CUDA graph per layer (7 linears = 7 kernels)", "parallelism": f"rows x{world}"},
-        "roofline": {"bound": "hbm", "kernel": "linear_tc_kernel<S=4,G=256,M=1,u16> 14336x4096",
+                   "launch": "CUDA graph per layer: 7 linears = 8 kernels (the K = 14336 linear quantises its activations in a "
+                             "small kernel of its own, the K = 4096 ones inside the GEMV)", "parallelism": f"rows x{world}"},
+        "roofline": {"bound": "hbm", "kernel": "linear_tcs_kernel<S=4,G=256,M=1,u16,KS=2> 14336x4096",
                      "achieved": round(achieved, 1), "peak": peak, "peak_kind": "of " + peak_kind, "unit": "GB/s",
                      "frac": round(achieved / peak, 4), "frac_of_nominal_8000": round(achieved / 8000.0, 4),
-                     "us_per_launch": round(dom_us, 2), "bytes_per_launch": dom_bytes, "traffic": TRAFFIC_DOMINANT},
+                     "us_per_launch": round(dom_us, 2), "us_per_launch_min": round(min(dom_all), 2),
+                     "us_per_launch_max": round(max(dom_all), 2), "bytes_per_launch": dom_bytes, "traffic": TRAFFIC_DOMINANT},
         "e2e": {"value": round(world * STEP_BYTES / (e2e_s / n_e2e) / 1e9, 1), "unit": "GB/s",
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_s / n_e2e * 1e3, 4),
                 "api": "sbvr.linear (python) -> sbvr_linear_f16 (C ABI), pinned host x in, pinned host y out; the step "
                        "(1 H2D copy of both activation rows, 7 linears, 1 D2H copy of the 7 results) is captured once and "
                        "replayed, then the stream is waited for"},
-        "gpu_launches": args.steps * len(SHAPES),
+        "gpu_launches": args.steps * (len(SHAPES) + 1),
+        "gpu_launches_note": f"per timed region of {args.steps} steps (8 kernels per step); the region is repeated {REPEATS} times",
         "clocks": clocks,
     }
     line.update(extra)
@@ -288,6 +312,87 @@ def run_ours(args):
     print(json.dumps(line), flush=True)
     if dist:
         dist.destroy_process_group()
+
+
+def strong_rows(torch, dev, dist, world, stream, gen):
+    """Strong scaling of ONE layer: every linear's output rows are split over the ranks (what the column-parallel
+    projections of a tensor-parallel model launch), no collective.  Aggregate GB/s = bytes of the whole layer / time of the
+    slowest rank; enough shard layers are cycled to exceed L2."""
+    import sbvr
+    shard = [(name, n // world, k) for name, n, k in SHAPES]
+    layer_bytes = sum(alg_bytes(1, n, k) for _, n, k in shard)
+    n_layers = max(4, int(2 * 126e6 / layer_bytes) + 1)
+
+    def mk(N, K):
+        bvr = torch.randint(-2**31, 2**31 - 1, (K // 32, N, S), dtype=torch.int32, device=dev, generator=gen)
+        idx = torch.randint(0, C, (K // G, N), device=dev, generator=gen).to(torch.int16).view(torch.uint16)
+        cache = (torch.randn((C, S), device=dev, generator=gen) * 0.01).half()
+        return sbvr.sbvr.from_packed(bvr, idx, cache, group_len=G, device=dev)
+    layers = [{name: mk(n, k) for name, n, k in shard} for _ in range(n_layers)]
+    xs = {k: torch.randn((1, k), device=dev, generator=gen).half() for k in {k for _, _, k in shard}}
+    outs = {name: torch.empty((1, n), dtype=torch.float16, device=dev) for name, n, _ in shard}
+    with torch.cuda.stream(stream):
+        def step(L):
+            for name, _, k in shard:
+                sbvr.linear(xs[k], L[name], None, out=outs[name])
+        for L in layers:
+            step(L)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            for L in layers:
+                step(L)
+        g.replay()
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(REPEATS):
+            dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            g.replay()
+            e1.record(stream)
+            e1.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            times.append(float(t.item()) * 1e3 / n_layers)
+    us = sorted(times)[len(times) // 2]
+    del layers
+    torch.cuda.empty_cache()
+    return {"what": "one llama3-8b layer, every linear's rows split over the ranks, M=1, no collective",
+            "us_per_layer": round(us, 2), "GBps_aggregate": round(STEP_BYTES / us / 1e3, 1),
+            "shard_shapes": [[n, k] for _, n, k in shard], "layers_cycled": n_layers}
+
+
+def tp_parity(torch, dev, dist, world):
+    """Correctness of the tensor-parallel model on this job's ranks: logits of a small model against the same model on one
+    rank (max relative error, rank 0), graph = eager tokens, and token agreement of the fused all-reduce path with NCCL."""
+    from models.sbvr_llama import LlamaConfig, SBVRLlamaForCausalLM
+    cfg = LlamaConfig.preset("tiny" if world <= 2 else "tiny8")
+    tp = SBVRLlamaForCausalLM(cfg, device=dev, tp_group=dist.group.WORLD, max_batch=2, max_ctx=64).init_synthetic(3)
+    ids = torch.randint(0, cfg.vocab_size, (2, 24), device=dev, generator=torch.Generator(device=dev).manual_seed(9))
+    logits = tp(ids).float()
+    a = tp.generate(ids, 10, use_graph=False)
+    b = tp.generate(ids, 10, use_graph=True)
+    res = {"model": "tiny" if world <= 2 else "tiny8", "tp": world, "graph_equals_eager": bool(torch.equal(a, b))}
+    if tp.enable_fused_allreduce(16):
+        c = tp.generate(ids, 10, use_graph=True)
+        res["fused_vs_nccl_token_agreement"] = round((c == a).float().mean().item(), 4)
+    else:
+        res["fused_allreduce"] = "unavailable: " + str(getattr(tp, "_comm_error", "?"))[:100]
+    err = torch.zeros(1, device=dev)
+    if dist.get_rank() == 0:
+        one = SBVRLlamaForCausalLM(cfg, device=dev, max_batch=2, max_ctx=64).init_synthetic(3)
+        ref = one(ids).float()
+        err[0] = (logits - ref).abs().max() / ref.abs().max()
+        del one
+    dist.all_reduce(err, op=dist.ReduceOp.MAX)
+    res["logits_max_rel_err_vs_one_rank"] = round(float(err.item()), 5)
+    res["tolerance"] = 1e-2
+    tp._check()
+    del tp
+    torch.cuda.empty_cache()
+    return res
 
 
 def graph_time_us(torch, stream, fns, reps=5):
@@ -311,9 +416,36 @@ def graph_time_us(torch, stream, fns, reps=5):
     return e0.elapsed_time(e1) * 1e3 / reps / len(fns)
 
 
+def median_graph_time_us(torch, stream, fns, reps=5, repeats=5):
+    """Median over `repeats` of graph_time_us-style measurements (one graph, `reps` replays per measurement)."""
+    with torch.cuda.stream(stream):
+        for f in fns:
+            f()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            for f in fns:
+                f()
+        g.replay()
+        torch.cuda.synchronize()
+        out = []
+        for _ in range(repeats):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(reps):
+                g.replay()
+            e1.record(stream)
+            e1.synchronize()
+            out.append(e0.elapsed_time(e1) * 1e3 / reps / len(fns))
+    return sorted(out)[len(out) // 2]
+
+
 def small_m_and_prefill(torch, dev, stream):
-    """The two neighbouring configurations beside the headline: the M sweep of the layer shapes (HBM roofline) and the
-    M = 2048 prefill GEMM (tensor roofline).  Every timing cycles through more weights than L2 holds."""
+    """The neighbouring configurations beside the headline: the M sweep of the layer shapes for 2, 3 and 4 bit-planes
+    (HBM roofline), the same at group length 128 with direct coefficients, the other formulations of the product (SIMT
+    dequantise-and-FMA kernel, popcount product of two encoded operands, the reference's own CUDA kernels where they
+    were built), the M = 2048 prefill GEMM (tensor roofline) and the encoder.  Every timing cycles through more weights
+    than L2 holds and is the median of five measurements."""
     import sbvr
     peak, _ = measured_peak()
     try:
@@ -322,39 +454,93 @@ def small_m_and_prefill(torch, dev, stream):
     except Exception:
         tf_peak = 1590.0
     gen = torch.Generator(device=dev).manual_seed(11)
+    shapes = [(4096, 4096), (1024, 4096), (14336, 4096), (4096, 14336)]
 
-    def mk(N, K):
-        bvr = torch.randint(-2**31, 2**31 - 1, (K // 32, N, S), dtype=torch.int32, device=dev, generator=gen)
-        idx = torch.randint(0, C, (K // G, N), device=dev, generator=gen).to(torch.int16).view(torch.uint16)
-        cache = (torch.randn((C, S), device=dev, generator=gen) * 0.01).half()
-        return sbvr.sbvr.from_packed(bvr, idx, cache, group_len=G, device=dev)
-    sweep, prefill, rowdeq = [], [], []
-    for N, K in [(4096, 4096), (1024, 4096), (14336, 4096), (4096, 14336)]:
+    def mk(N, K, s=S, g=G, direct=False):
+        bvr = torch.randint(-2**31, 2**31 - 1, (K // 32, N, s), dtype=torch.int32, device=dev, generator=gen)
+        if direct:
+            coeff = (torch.randn((K // g, N, s), device=dev, generator=gen) * 0.01).half()
+            return sbvr.sbvr.from_packed(bvr, None, coeff, group_len=g, device=dev)
+        idx = torch.randint(0, C, (K // g, N), device=dev, generator=gen).to(torch.int16).view(torch.uint16)
+        cache = (torch.randn((C, s), device=dev, generator=gen) * 0.01).half()
+        return sbvr.sbvr.from_packed(bvr, idx, cache, group_len=g, device=dev)
+
+    def row(N, K, M, s, g, us, ib, algo=None):
+        byt = alg_bytes(M, N, K, s=s, g=g, ib=ib, c=(C if ib else 0)) if ib else \
+            N * K * s // 8 + N * (K // g) * s * 2 + M * K * 2 + M * N * 2
+        gbs = byt / us / 1e3
+        r = {"N": N, "K": K, "M": M, "S": s, "G": g, "us": round(us, 2), "GBps": round(gbs, 1), "frac": round(gbs / peak, 4)}
+        if algo is not None:
+            r["algo"] = algo
+        return r
+
+    sweep, prefill, rowdeq, direct128, others = [], [], [], [], []
+    for N, K in shapes:
+        for s in (4, 3, 2):
+            ncopy = int(2 * 126e6 / (N * K * s / 8)) + 2
+            ws_ = [mk(N, K, s=s) for _ in range(ncopy)]
+            for M in ((1, 4, 16, 32) if s == 4 else (1, 16)):
+                x = torch.randn((M, K), device=dev, generator=gen).half()
+                outs = [torch.empty((M, N), dtype=torch.float16, device=dev) for _ in range(ncopy)]
+                us = median_graph_time_us(torch, stream, [(lambda w=w, o=o: sbvr.linear(x, w, None, out=o)) for w, o in zip(ws_, outs)])
+                sweep.append(row(N, K, M, s, G, us, IDXB))
+            if s == 4:
+                x = torch.randn((1, K), device=dev, generator=gen).half()
+                outs = [torch.empty((1, N), dtype=torch.float16, device=dev) for _ in range(ncopy)]
+                us = median_graph_time_us(torch, stream, [(lambda w=w, o=o: sbvr.linear(x, w, None, algo=1, out=o)) for w, o in zip(ws_, outs)], reps=2, repeats=3)
+                others.append(dict(row(N, K, 1, 4, G, us, IDXB, algo=1), kernel="SIMT dequantise-and-FMA (linear_simt_kernel)"))
+            if s == 4 and N * K == 14336 * 4096:
+                M = 2048
+                x = torch.randn((M, K), device=dev, generator=gen).half()
+                out = torch.empty((M, N), dtype=torch.float16, device=dev)
+                us = median_graph_time_us(torch, stream, [(lambda w=w: sbvr.linear(x, w, None, out=out)) for w in ws_[:4]])
+                tf = 2.0 * M * N * K / us / 1e6
+                prefill.append({"N": N, "K": K, "M": M, "us": round(us, 1), "TFLOPs": round(tf, 1),
+                                "frac_of_measured_bf16_burst": round(tf / tf_peak, 4)})
+            del ws_
+        # group length 128, one coefficient line per (group, row): the configuration the task sheet words (the reference
+        # itself hard-wires 256)
         ncopy = int(2 * 126e6 / (N * K * S / 8)) + 2
-        ws_ = [mk(N, K) for _ in range(ncopy)]
-        for M in (1, 4, 16, 32):
+        wd_ = [mk(N, K, g=128, direct=True) for _ in range(ncopy)]
+        for M in (1, 16):
             x = torch.randn((M, K), device=dev, generator=gen).half()
             outs = [torch.empty((M, N), dtype=torch.float16, device=dev) for _ in range(ncopy)]
-            us = graph_time_us(torch, stream, [(lambda w=w, o=o: sbvr.linear(x, w, None, out=o)) for w, o in zip(ws_, outs)])
-            gbs = alg_bytes(M, N, K) / us / 1e3
-            sweep.append({"N": N, "K": K, "M": M, "us": round(us, 2), "GBps": round(gbs, 1), "frac": round(gbs / peak, 4)})
-        if N * K == 14336 * 4096:
-            M = 2048
-            x = torch.randn((M, K), device=dev, generator=gen).half()
-            out = torch.empty((M, N), dtype=torch.float16, device=dev)
-            us = graph_time_us(torch, stream, [(lambda w=w: sbvr.linear(x, w, None, out=out)) for w in ws_[:4]])
-            tf = 2.0 * M * N * K / us / 1e6
-            prefill.append({"N": N, "K": K, "M": M, "us": round(us, 1), "TFLOPs": round(tf, 1),
-                            "frac_of_measured_bf16_burst": round(tf / tf_peak, 4)})
-        del ws_
+            us = median_graph_time_us(torch, stream, [(lambda w=w, o=o: sbvr.linear(x, w, None, out=o)) for w, o in zip(wd_, outs)])
+            direct128.append(row(N, K, M, S, 128, us, 0))
+        del wd_
         # the same product on the transposed ("row-dequant") encoding: packed W^T, groups along the output dimension
         wt_ = [mk(K, N) for _ in range(ncopy)]
         for M in (1, 4):
             x = torch.randn((M, K), device=dev, generator=gen).half()
-            us = graph_time_us(torch, stream, [(lambda w=w: sbvr.row_deq_mm_T(x, w)) for w in wt_])
-            gbs = alg_bytes(M, N, K) / us / 1e3
-            rowdeq.append({"N": N, "K": K, "M": M, "us": round(us, 2), "GBps": round(gbs, 1), "frac": round(gbs / peak, 4)})
+            us = median_graph_time_us(torch, stream, [(lambda w=w: sbvr.row_deq_mm_T(x, w)) for w in wt_])
+            rowdeq.append(row(N, K, M, S, G, us, IDXB))
+        # ... and the reference's own kernel for it, compiled for this GPU, on the same tensors (default stream, no graph)
+        try:
+            from oracle import ref_cuda
+            if ref_cuda.lib() is not None:
+                x = torch.randn((1, K), device=dev, generator=gen).half()
+                us = sum(ref_cuda.time_row_deq_us(x, w.bvr, w.coeff_idx, w.coeff_cache, reps=3) for w in wt_) / len(wt_)
+                others.append(dict(row(N, K, 1, S, G, us, IDXB), kernel="reference cuda_1xtN_rd_WP8_TBW4_NS4 (transposed "
+                                   "layout, compiled unchanged for sm_100)"))
+        except Exception as e:                                  # the comparator is optional
+            others.append({"N": N, "K": K, "kernel": "reference row-dequant kernel", "unavailable": str(e)[:120]})
         del wt_
+    # popcount product of two encoded operands (the reference's `_sbvr_mm_T`), one encoded activation row
+    for N, K in [(4096, 4096), (14336, 4096)]:
+        ncopy = int(2 * 126e6 / (N * K * S / 8)) + 2
+        rs_ = [mk(N, K) for _ in range(ncopy)]
+        a = mk(1, K)
+        us = median_graph_time_us(torch, stream, [(lambda w=w: sbvr.mm_T(a, w)) for w in rs_])
+        others.append(dict(row(N, K, 1, S, G, us, IDXB), kernel="popcount product, both operands encoded (popc_mm_kernel)"))
+        try:
+            from oracle import ref_cuda
+            if ref_cuda.lib() is not None:
+                us = sum(ref_cuda.time_mm_T_us(a.bvr, a.coeff_idx, a.coeff_cache, w.bvr, w.coeff_idx, w.coeff_cache, reps=5)
+                         for w in rs_) / len(rs_)
+                others.append(dict(row(N, K, 1, S, G, us, IDXB), kernel="reference cuda_1xtN_sbvr_mm_T (compiled unchanged for sm_100)"))
+        except Exception as e:
+            others.append({"N": N, "K": K, "kernel": "reference popcount kernel", "unavailable": str(e)[:120]})
+        del rs_
     # the encoder: a 4096 x 4096 weight (randn * 0.02, the reference's recipe) to packed form, wall clock including the host walk
     import time
     Wd = (torch.randn((4096, 4096), device=dev, generator=gen) * 0.02).half()
@@ -367,7 +553,9 @@ def small_m_and_prefill(torch, dev, stream):
     rel = float(((we.decode().float() - Wd.float()) ** 2).mean() / (Wd.float() ** 2).mean())
     enc = {"shape": [4096, 4096], "S": S, "seconds": round(dt, 3), "groups_per_s": round(65536 / dt),
            "relative_mse": round(rel, 5), **we.encoder_stats}
-    return {"small_m_sweep": {"S": S, "G": G, "rows": sweep}, "prefill_gemm": prefill,
+    return {"small_m_sweep": {"G": G, "index": "u16 codebook C=4096", "rows": sweep},
+            "group128_direct": {"rows": direct128},
+            "other_formulations_m1": others, "prefill_gemm": prefill,
             "row_deq_transposed_layout": {"S": S, "G": G, "rows": rowdeq}, "encoder": enc}
 
 
@@ -438,46 +626,60 @@ def llama_decode(torch, dev, dist, world, preset, batch, prompt, new_tokens):
     return res
 
 
-def cpu_baseline(reps=None):
-    """The CPU port of the reference arithmetic (oracle/sbvr_oracle.c, OpenMP over output rows), timed on
-    this host on a bounded sample of the workload: the q-projection shape (4096 x 4096, 8.6 MB)."""
+def cpu_layer_step(O, np, packed, xs):
+    """One STEP of the workload on the CPU port: the seven linears of the layer, each on its own packed weight."""
+    for name, N, K in SHAPES:
+        p = packed[(N, K)]
+        O.linear_c(xs[K], p["bvr"], p["coeff_idx"], p["coeff"], G=G)
+
+
+def cpu_baseline(steps=None, budget_s=10.0):
+    """The CPU port of the reference arithmetic (oracle/sbvr_oracle.c: fused decode + dot with fp32 accumulation, OpenMP over
+    output rows; the reference's own native kernels are ARM-NEON code that does not build on this host), timed on this
+    host's cores on whole STEPS of the workload: all four layer shapes, seven linears per step.  `steps` fixes the number
+    of steps; otherwise steps are run until about `budget_s` seconds have passed."""
     import numpy as np
     from oracle import sbvr_oracle as O
-    N, K = 4096, 4096
-    p = O.make_packed(N, K, S, G=G, mode="u16", C=C, seed=7)
-    x = np.random.default_rng(1).standard_normal((1, K)).astype(np.float16)
+    packed = {(N, K): O.make_packed(N, K, S, G=G, mode="u16", C=C, seed=7 + i) for i, (N, K) in
+              enumerate(sorted({(n, k) for _, n, k in SHAPES}))}
+    rng = np.random.default_rng(1)
+    xs = {K: rng.standard_normal((1, K)).astype(np.float16) for K in {k for _, _, k in SHAPES}}
     O.c_lib().sbvr_oracle_set_threads(os.cpu_count() or 1)      # torchrun exports OMP_NUM_THREADS=1
     threads = O.c_lib().sbvr_oracle_threads()
-    O.linear_c(x, p["bvr"], p["coeff_idx"], p["coeff"], G=G)
+    cpu_layer_step(O, np, packed, xs)                            # warm-up
     t0 = time.perf_counter()
     n = 0
     while True:
-        O.linear_c(x, p["bvr"], p["coeff_idx"], p["coeff"], G=G)
+        cpu_layer_step(O, np, packed, xs)
         n += 1
         el = time.perf_counter() - t0
-        if (reps and n >= reps) or (not reps and (el > 10.0 or n >= 200)):
+        if (steps and n >= steps) or (not steps and (el > budget_s or n >= 1000)):
             break
-    gbs = alg_bytes(1, N, K) * n / el / 1e9
+    gbs = STEP_BYTES * n / el / 1e9
     return {"value": round(gbs, 3), "unit": "GB/s", "cores": threads, "kind": "port",
-            "sample": f"{n} x SBVR linear 4096x4096 S=4 G=256 M=1 (fused decode + dot, fp32 accumulate), "
-                      f"{el / n * 1e3:.2f} ms each"}
+            "sample": f"{n} whole steps (7 SBVR linears of the layer: 4096x4096 x2, 1024x4096 x2, 14336x4096 x2, "
+                      f"4096x14336; S=4 G=256 M=1), {el / n * 1e3:.2f} ms per step",
+            "ms_per_step": round(el / n * 1e3, 3)}
 
 
 def run_reference(args):
-    """The reference's own way of running this path on a CPU is `x @ decode().T` (its native kernels are
-    ARM-NEON only and take encoded activations); the C port of that arithmetic is what can run here."""
+    """The reference's own way of running this path on a CPU is `x @ decode().T` (its native kernels are ARM-NEON only and
+    take encoded activations); the C port of that arithmetic is what can run here.  Same workload, metric and unit as the
+    GPU arm: whole steps of the seven layer linears, all host threads."""
     if int(os.environ.get("RANK", "0")) != 0:
         return
     t_all = time.perf_counter()
-    base = cpu_baseline(reps=max(args.steps, 1) * 4)
+    steps = max(1, min(args.steps, 300))                         # 300 steps are about 20 s of CPU work
+    base = cpu_baseline(steps=steps)
     v = base["value"]
     line = {"metric": "sbvr_gemv_hbm_gbs_m1", "value": v, "unit": "GB/s", "impl": "reference",
             "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": round(STEP_BYTES / (v * 1e9) * 1e3, 3), "higher_is_better": True, "scaling": "weak",
+            "ms_per_step": base["ms_per_step"], "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": "llama3-8b decoder-layer linears (q,k,v,o,gate,up,down), M=1, S=4, G=256, "
                                    "u16 codebook C=4096", "bytes_per_step": STEP_BYTES,
-                       "note": "bounded sample: the 4096x4096 linear; ms_per_step is scaled to the step's bytes"},
+                       "note": f"CPU port of the reference arithmetic on all host threads; {steps} whole steps timed "
+                               "(bounded at 300)"},
             "cpu_baseline": base,
             "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "wall_s": round(time.perf_counter() - t_all, 1)}
