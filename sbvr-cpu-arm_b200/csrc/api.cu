@@ -136,7 +136,14 @@ int sbvr_workspace_bytes(int device, int M, int N, int K, size_t* bytes) {
     w.N = N, w.K = K, w.S = 4, w.G = 256;
     const size_t fixed = SBVR_WS_FIXED_BYTES;
     const size_t stage = (((size_t)M * K * 2 + 255) / 256 + ((size_t)M * N * 2 + 255) / 256) * 256;   // host-pointer staging
-    *bytes = fixed + linear_gemm_workspace_bytes(w, M, di.sm_count) + stage + ((size_t)8 << 20);
+    size_t kern = linear_gemm_workspace_bytes(w, M, di.sm_count);
+    if (M >= 2 && M <= 32) {                       // the small-batch kernel's digits and partial sums (two planes: widest tiles)
+        w.S = 2;
+        const size_t tcb = linear_tcb_workspace_bytes(w, M, di.sm_count);
+        w.S = 4;
+        if (tcb > kern) kern = tcb;
+    }
+    *bytes = fixed + kern + stage + ((size_t)8 << 20);
     if (*bytes < ((size_t)32 << 20)) *bytes = (size_t)32 << 20;
     return SBVR_OK;
 }
@@ -186,7 +193,7 @@ int sbvr_linear_f16(const void* x, const uint32_t* bvr, const void* coeff_idx, i
     if (rc) return rc;
     if (!x || !y || M < 1) return SBVR_ERR_BAD_ARG;
     if ((reinterpret_cast<uintptr_t>(x) & 3) || (reinterpret_cast<uintptr_t>(y) & 1)) return SBVR_ERR_ALIGN;
-    if (algo < 0 || algo > 3) return SBVR_ERR_BAD_ARG;
+    if (algo < 0 || algo > 4) return SBVR_ERR_BAD_ARG;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     const __half* xh = reinterpret_cast<const __half*>(x);
     const __half* bh = reinterpret_cast<const __half*>(bias);
@@ -206,6 +213,10 @@ int sbvr_linear_f16(const void* x, const uint32_t* bvr, const void* coeff_idx, i
         return launch_linear_tcs(xh, w, bh, yh, M, ws->device, ws->status, ws->xchg, ws->dyn, ws->dyn_bytes, st);
     }
     if (algo == 3) return launch_linear_gemm(xh, w, bh, yh, M, ws, st);
+    if (algo == 4) {
+        if (!ws) return SBVR_ERR_WORKSPACE;
+        return launch_linear_tcb(xh, w, bh, yh, M, ws->device, ws->status, ws->xchg, ws->dyn, ws->dyn_bytes, st);
+    }
     return launch_linear_simt(xh, w, bh, yh, M, st);
 }
 

@@ -121,6 +121,12 @@ size_t linear_tcs_workspace_bytes(const PackedW& w, int M, int sm_count);
 int launch_linear_tcs(const __half* x, const PackedW& w, const __half* bias, __half* y, int M, int device,
                       unsigned int* status, unsigned long long* xchg, char* scratch, size_t scratch_bytes, cudaStream_t st,
                       const XOp* xop = nullptr);
+// The small-batch kernel (linear_tcb.cu), 2 .. 32 activation rows: same scratch rules; it uses the first words of the
+// exchange region as arrival counters and leaves them zero.
+bool linear_tcb_supported(const PackedW& w, int M);
+size_t linear_tcb_workspace_bytes(const PackedW& w, int M, int sm_count);
+int launch_linear_tcb(const __half* x, const PackedW& w, const __half* bias, __half* y, int M, int device,
+                      unsigned int* status, unsigned long long* xchg, char* scratch, size_t scratch_bytes, cudaStream_t st);
 bool linear_gemm_supported(const PackedW& w, int M);
 size_t linear_gemm_workspace_bytes(const PackedW& w, int M, int sm_count);
 int launch_linear_gemm(const __half* x, const PackedW& w, const __half* bias, __half* y, int M,

@@ -454,3 +454,64 @@ def test_small_batches_llama_shapes(shape, M, S):
     assert err <= TOL, err
     assert err <= 3e-3, err
     check_status()
+
+
+@pytest.mark.parametrize("S", [2, 3, 4])
+@pytest.mark.parametrize("G,mode", [(256, "u16"), (128, "u8"), (256, "direct"), (128, "direct")])
+@pytest.mark.parametrize("M", [2, 5, 8, 15, 16, 17, 24, 31, 32])
+def test_linear_small_batch_kernel_grid(S, G, mode, M):
+    """The small-batch tensor-core kernel (algo 4) against the oracle: both digit packings (M <= 16 and M > 16), ragged M,
+    every plane count and coefficient form, few tiles (k blocks of a tile group spread over CTAs) and a ragged tile group."""
+    import sbvr
+    if G == 128 and M > 16:
+        pytest.skip("two groups per 256-k block: up to 16 activation rows on this kernel")
+    N, K = 320, 1536
+    p = O.make_packed(N, K, S, G=G, mode=mode, seed=S * 1000 + G + M)
+    w = to_sbvr(p)
+    rng = np.random.default_rng(M)
+    x = rng.standard_normal((M, K)).astype(np.float16)
+    x[:, ::5] *= 16.0                                   # a few large activations per block: small ones keep their low bits
+    b = (rng.standard_normal(N) * 0.3).astype(np.float16)
+    ref = O.linear_c(x, p["bvr"], p["coeff_idx"], p["coeff"], bias=b, G=G)
+    xt, bt = torch.from_numpy(x).cuda(), torch.from_numpy(b).cuda()
+    y = sbvr.linear(xt, w, bt, algo=4)
+    err = O.max_rel_err(h2n(y), ref)
+    assert err <= TOL, err
+    assert err <= 3e-3, err
+    assert torch.equal(y, sbvr.linear(xt, w, bt, algo=4))          # fixed summation order: the same bits on every run
+    check_status()
+
+
+@pytest.mark.parametrize("shape", [(4096, 4096), (1024, 4096), (14336, 4096), (4096, 14336)])
+@pytest.mark.parametrize("M", [5, 16, 32])
+def test_linear_small_batch_kernel_llama_shapes(shape, M):
+    """Algo 4 on the four layer shapes."""
+    import sbvr
+    N, K = shape
+    p = O.make_packed(N, K, 4, G=256, mode="u16", C=4096, seed=M + N // 1024)
+    w = to_sbvr(p)
+    rng = np.random.default_rng(M + K)
+    x = rng.standard_normal((M, K)).astype(np.float16)
+    ref = O.linear_c(x, p["bvr"], p["coeff_idx"], p["coeff"], G=256)
+    xt = torch.from_numpy(x).cuda()
+    y = sbvr.linear(xt, w, None, algo=4)
+    err = O.max_rel_err(h2n(y), ref)
+    assert err <= TOL, err
+    assert err <= 3e-3, err
+    check_status()
+
+
+def test_small_batch_kernel_non_finite_row_poisons_only_that_row():
+    import sbvr
+    N, K, M = 256, 1024, 6
+    p = O.make_packed(N, K, 4, G=256, mode="u16", C=4096, seed=77)
+    w = to_sbvr(p)
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((M, K)).astype(np.float16)
+    ref = O.linear_c(x, p["bvr"], p["coeff_idx"], p["coeff"], G=256)
+    x[2, 700] = np.inf
+    y = h2n(sbvr.linear(torch.from_numpy(x).cuda(), w, None, algo=4))
+    assert np.isnan(y[2]).all()
+    keep = [0, 1, 3, 4, 5]
+    assert O.max_rel_err(y[keep], ref[keep]) <= TOL
+    check_status()
