@@ -97,7 +97,11 @@ SBVR_API int sbvr_decode_f16(const uint32_t* bvr, const void* coeff_idx, int idx
  *       memory), bvr / coeff_idx / coeff / x 16-byte aligned; needs a workspace: status word, activation digits,
  *       partial sums);
  *   3 = tcgen05 fp16 GEMM with in-kernel dequantisation for batches and prefill (S in {2,3,4}, any M,
- *       N a multiple of 128; needs a workspace of sbvr_workspace_bytes(...)). */
+ *       N a multiple of 128; needs a workspace of sbvr_workspace_bytes(...));
+ *   4 = tcgen05 FP4 tensor-core kernel for small batches (2 <= M <= 32, at most 16 for G = 128; S, G, N and alignment as
+ *       for algo 2, K a multiple of 256 and at most 32768; the activations are quantised by a small kernel in front;
+ *       needs a workspace of sbvr_workspace_bytes(...)).  Picked by algo 0 for 5 <= M <= 16 on weights large enough
+ *       to give every SM eight (three-tile group, 256-k block) steps. */
 SBVR_API int sbvr_linear_f16(const void* x, const uint32_t* bvr, const void* coeff_idx, int idx_bytes, const void* coeff,
                     int C, const void* bias, void* y, int M, int N, int K, int S, int G, int algo,
                     sbvr_workspace_t* ws, sbvr_stream_t stream);

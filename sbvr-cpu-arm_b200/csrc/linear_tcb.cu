@@ -23,9 +23,14 @@
 // blob the quantiser kernel wrote) serves all of them.  Per warpgroup an issuer warp streams the packed words (TMA) and
 // issues the MMAs; the compute warps expand step i, write its B scale factors to tensor memory, and read the sums of
 // step i - 2.  Work is split by (tile group, k block) steps over the CTAs like the decode GEMV's; a tile group whose k
-// blocks are spread over several CTAs is finished by the first of them from fp32 partial sums in scratch, summed in
-// CTA order (the same bits on every run) once per-slot arrival counters (zero between calls) show them complete.
-// Every wait is bounded.
+// blocks are spread over several CTAs is finished by the first of them, after its own steps, from fp32 partial sums in
+// scratch, summed in CTA order (the same bits on every run) once per-slot arrival counters (zero between calls) show
+// them complete.  Every wait is bounded.
+//
+// Measured (B200, rotating weights larger than L2, CUDA graph, quantiser kernel included): 14336 x 4096, S = 4:
+// 26 us at M = 2, 28.7 us at M = 16, 36 us at M = 32 (the fp16 GEMM with in-kernel dequantisation: 34-35 us); a step of
+// three tiles takes about 1 500 cycles, bound by the latency chain of a compute warp (barrier, tensor-memory load,
+// expansion, store drain), not by the tensor pipe (12 or 24 MMAs of 17 cycles) nor by memory.
 //
 // Replaces the M > 1 use of `_sbvr_row_deq_mm_T` (reference sbvr/kernels/sbvr_kernel.cu:121-191) for 2 .. 32 rows.
 #include <cuda.h>
@@ -36,6 +41,7 @@
 #include "tc_stream.cuh"
 
 namespace sbvr {
+
 
 constexpr int TB_SF_BYTES = 512;                // 32 rows x 16 B of B scale factors (and the poison mask) per k block
 constexpr int TB_CW0 = 4;                       // first compute warp
@@ -173,6 +179,8 @@ __global__ void __launch_bounds__(tb_threads(NSUB), 1)
     uint64_t* tmem_ready = cache_bar + 1;
     uint64_t* sf_ready = tmem_ready + 1;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + TS_HDR - 64);
+    volatile int* done_cnt = reinterpret_cast<volatile int*>(smem + TS_HDR - 48);     // [2] compute warps done with a shared tile group
+    volatile int* ctab = reinterpret_cast<volatile int*>(smem + 448);                 // [128] who contributed to a shared tile group
     uint32_t* tmem_base_s = reinterpret_cast<uint32_t*>(smem + TS_HDR - 16);
 
     const int KB = p.KB, N = p.N, M = p.M;
@@ -195,7 +203,11 @@ __global__ void __launch_bounds__(tb_threads(NSUB), 1)
             if (i >= NB_A + NB_M + TB_MAX_BSTAGES && i < NB_A + NB_M + 2 * TB_MAX_BSTAGES) count = (uint32_t)NWG;    // b_empty
             if (i == NB - 1) count = 4u;                                                                           // sf_ready
             mbar_init(&a_full[i], count);
-            if (i == 0) *abort_flag = 0;
+            if (i == 0) {
+                *abort_flag = 0;
+                done_cnt[0] = 0;
+                done_cnt[1] = 0;
+            }
             fence_mbar_init();
         }
     }
@@ -418,49 +430,53 @@ __global__ void __launch_bounds__(tb_threads(NSUB), 1)
             }
         };
 
-        TsCursor fc;
-        fc.start(sg, 0);
+        int seg_q = 0, seg_left = sg.nseg > 0 ? sg.k1(0) - sg.k0(0) : 0;      // current segment, steps left in it
         float c1[NSUB], c2[NSUB];
         int fin1 = -1, fin2 = -1;
 #pragma unroll
         for (int sub = 0; sub < NSUB; ++sub) c1[sub] = c2[sub] = 0.0f;
         int aslot = 0, bslot = 0;
         uint32_t apar = 0u, bpar = 0u;
+        // What step i needs from shared memory is fetched during iteration i - 1, behind the tensor-memory stores of
+        // step i - 1 that have to drain anyway: packed words, coefficients, this lane's B scale factors.
+        uint32_t wv_n[8];
+        float cf_n[NSUB];
+        uint4 sf_n = make_uint4(0u, 0u, 0u, 0u);
+        auto fetch_next = [&](int i) {
+            ts_wait(full_ws + (uint32_t)aslot * 8u, apar, abort_flag, p.status, 0x432u);
+            const unsigned char* stg = ring_w + (size_t)aslot * TB_ASTAGE;
+            const uint32_t* wsrc = reinterpret_cast<const uint32_t*>(stg) + wpos;
+#pragma unroll
+            for (int kw = 0; kw < 8; ++kw) wv_n[kw] = live_row ? wsrc[kw * (WROW / 4)] : 0u;
+#pragma unroll
+            for (int sub = 0; sub < NSUB; ++sub) {
+                const unsigned char* cs = stg + COEF_OFF + sub * CI_BYTES;
+                float c = 0.0f;
+                if constexpr (IDXB == 0) {
+                    if (live_row) c = __half2float(reinterpret_cast<const __half*>(cs)[nl * S + s]);
+                } else {
+                    const uint32_t ci = (IDXB == 1) ? (uint32_t)cs[nl] : (uint32_t)reinterpret_cast<const unsigned short*>(cs)[nl];
+                    if (live_row) c = __half2float((p.cache_in_smem ? cache_s : p.coeff)[(size_t)ci * S + s]);
+                }
+                cf_n[sub] = c;
+            }
+            ts_wait(smem_u32(&b_full[bslot]), bpar, abort_flag, p.status, 0x433u);
+            sf_n = reinterpret_cast<const uint4*>(bring + (size_t)bslot * BSTAGE + NJ * 4096)[lane];
+            if (++aslot == AST) {
+                aslot = 0;
+                apar ^= 1u;
+            }
+            if (++bslot == BST) {
+                bslot = 0;
+                bpar ^= 1u;
+            }
+        };
+        if (n_steps > 0) fetch_next(0);
 #pragma unroll 1
         for (int i = 0; i < n_steps + 2; ++i) {
             const int buf = i & 1;
             const bool front = i < n_steps, back = i >= 2;
-            uint32_t wv[8];
-            uint32_t craw[NSUB];
-            uint4 sfrow = make_uint4(0u, 0u, 0u, 0u);
             int fin_i = -1;
-            if (front) {
-                ts_wait(full_ws + (uint32_t)aslot * 8u, apar, abort_flag, p.status, 0x432u);
-                const int q_i = fc.q;
-                fc.advance(sg, 1);
-                if (fc.done(sg) || fc.q != q_i) fin_i = q_i;
-                const unsigned char* stg = ring_w + (size_t)aslot * TB_ASTAGE;
-                const uint32_t* wsrc = reinterpret_cast<const uint32_t*>(stg) + wpos;
-#pragma unroll
-                for (int kw = 0; kw < 8; ++kw) wv[kw] = live_row ? wsrc[kw * (WROW / 4)] : 0u;
-#pragma unroll
-                for (int sub = 0; sub < NSUB; ++sub) {
-                    const unsigned char* cs = stg + COEF_OFF + sub * CI_BYTES;
-                    if constexpr (IDXB == 0) craw[sub] = live_row ? (uint32_t)reinterpret_cast<const unsigned short*>(cs)[nl * S + s] : 0u;
-                    else if constexpr (IDXB == 1) craw[sub] = (uint32_t)cs[nl];
-                    else craw[sub] = (uint32_t)reinterpret_cast<const unsigned short*>(cs)[nl];
-                }
-                ts_wait(smem_u32(&b_full[bslot]), bpar, abort_flag, p.status, 0x433u);
-                sfrow = reinterpret_cast<const uint4*>(bring + (size_t)bslot * BSTAGE + NJ * 4096)[lane];
-                if (++aslot == AST) {
-                    aslot = 0;
-                    apar ^= 1u;
-                }
-                if (++bslot == BST) {
-                    bslot = 0;
-                    bpar ^= 1u;
-                }
-            }
             uint32_t d[NSUB][4][8];
             if (back) {
                 ts_wait(mbar0 + buf * 8, (uint32_t)(((i >> 1) - 1) & 1), abort_flag, p.status, 0x434u);
@@ -473,20 +489,17 @@ __global__ void __launch_bounds__(tb_threads(NSUB), 1)
             }
             float cf[NSUB];
             if (front) {
-#pragma unroll
-                for (int sub = 0; sub < NSUB; ++sub) {
-                    float c = 0.0f;
-                    if constexpr (IDXB == 0) {
-                        c = __half2float(__ushort_as_half((unsigned short)craw[sub]));
-                    } else {
-                        if (live_row) c = __half2float((p.cache_in_smem ? cache_s : p.coeff)[(size_t)craw[sub] * S + s]);
-                    }
-                    cf[sub] = c;
+                if (--seg_left == 0) {               // last step of a segment: its sums are finished two iterations later
+                    fin_i = seg_q;
+                    ++seg_q;
+                    seg_left = seg_q < sg.nseg ? sg.k1(seg_q) - sg.k0(seg_q) : 0;
                 }
+#pragma unroll
+                for (int sub = 0; sub < NSUB; ++sub) cf[sub] = cf_n[sub];
                 // packed words of this thread's row -> 32 words of 4-bit elements {0, 1 | 1 | 2 | 2}
 #pragma unroll
                 for (int h = 0; h < 4; ++h) {
-                    const uint32_t w0 = wv[2 * h], w1 = wv[2 * h + 1];
+                    const uint32_t w0 = wv_n[2 * h], w1 = wv_n[2 * h + 1];
                     ts_st8(a_addr + buf * 32 + h * 8, (w0 << 1) & 0x22222222u, w0 & 0x22222222u, w0 & 0x44444444u,
                            (w0 >> 1) & 0x44444444u, (w1 << 1) & 0x22222222u, w1 & 0x22222222u, w1 & 0x44444444u,
                            (w1 >> 1) & 0x44444444u);
@@ -495,9 +508,10 @@ __global__ void __launch_bounds__(tb_threads(NSUB), 1)
                 asm volatile(
                     "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%4,%4,%4,%2,%4,%4,%4,%3,%4,%4,%4,%4,%4,%4,%4};" ::"r"(
                         sfb_addr + buf * 16),
-                    "r"(sfrow.x), "r"(sfrow.y), "r"(sfrow.z), "r"(0x7F7F7F7Fu)
+                    "r"(sf_n.x), "r"(sf_n.y), "r"(sf_n.z), "r"(0x7F7F7F7Fu)
                     : "memory");
-                pm |= sfrow.w;
+                pm |= sf_n.w;
+                if (i + 1 < n_steps) fetch_next(i + 1);
             }
             if (back) {
 #pragma unroll
@@ -535,42 +549,75 @@ __global__ void __launch_bounds__(tb_threads(NSUB), 1)
             if (q < 0) continue;
             const int rt = sg.tile(q) - sg.rem_tile0;
             const int tile = sg.tile(q) * NWG + w;
-            // all contributors have delivered: lanes look at the owners of different steps
-            {
-                const long long t0 = clock64();
+            // Who contributed: the first compute warp works out the owners of the tile group's steps, one step per lane
+            // and round (the divisions of cta_of / slot_of cost about 200 cycles each), leaves slot index + 1 of a step's
+            // owner in shared memory (0 where the owner is that of the step before), waits until every contributor has
+            // delivered, and releases the other compute warps.  All lanes stay converged: a warp that had diverged in
+            // per-lane polling loops needed about 800 cycles for every later shuffle.
+            const int self_ent = (int)blockIdx.x * 2 + sg.slot_of(blockIdx.x, rt) + 1;
+            if (warp == CW0) {
                 for (int k = lane; k < KB; k += 32) {
                     const int cc = sg.cta_of((unsigned int)(rt * KB + k));
-                    if (cc == (int)blockIdx.x) continue;
-                    const unsigned int* f = p.flags + cc * 2 + sg.slot_of((unsigned int)cc, rt);
-                    for (;;) {
-                        unsigned int got;
-                        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(got) : "l"(f) : "memory");
-                        if (got >= (unsigned int)(4 * NWG) || *abort_flag) break;
-                        if (clock64() - t0 > 2000000000LL) {
-                            *abort_flag = 1;
-                            atomicExch(p.status, 1u);
-                            atomicExch(p.status + 1, 0x440u);
-                            break;
-                        }
-                    }
+                    const int cp = k > 0 ? sg.cta_of((unsigned int)(rt * KB + k - 1)) : -1;
+                    ctab[k] = (cc != cp) ? cc * 2 + sg.slot_of((unsigned int)cc, rt) + 1 : 0;
                 }
                 __syncwarp();
+                const long long t0 = clock64();
+                for (;;) {
+                    bool ok = true;
+                    for (int k = lane; k < KB; k += 32) {
+                        const int en = ctab[k];
+                        if (en != 0 && en != self_ent) {
+                            unsigned int got;
+                            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(got) : "l"(p.flags + (en - 1)) : "memory");
+                            ok = ok && got >= (unsigned int)(4 * NWG);
+                        }
+                    }
+                    if (__all_sync(0xffffffffu, ok) || *abort_flag) break;
+                    if (clock64() - t0 > 2000000000LL) {
+                        *abort_flag = 1;
+                        atomicExch(p.status, 1u);
+                        atomicExch(p.status + 1, 0x440u);
+                        break;
+                    }
+                }
+                __threadfence();
             }
+            named_bar_sync(14, NWG * 128);         // the list is complete and every contributor's sums are visible
+            // The sums are added in step order, eight contributors at a time with all their loads in flight.  This code
+            // runs once per kernel, so its instructions come from L2: a batch of sixteen (twice the code) took 10 000 cycles.
             float v[NV];
 #pragma unroll
             for (int e = 0; e < NV; ++e) v[e] = 0.0f;
-            int prev = -1;
+            int k = 0;
 #pragma unroll 1
-            for (int k = 0; k < KB; ++k) {
-                const int cc = sg.cta_of((unsigned int)(rt * KB + k));
-                if (cc == prev) continue;
-                prev = cc;
-                const float* src = p.part + (((size_t)cc * 2 + sg.slot_of((unsigned int)cc, rt)) * NWG + w) * (MP * TN);
-                float t[NV];
+            while (k < KB) {
+                const float* src[8];
+                int n = 0;
 #pragma unroll
-                for (int e = 0; e < NV; ++e) t[e] = __ldcg(src + (e * SP + s) * TN + nl);
+                for (int j = 0; j < 8; ++j) src[j] = p.part;
+#pragma unroll 1
+                while (k < KB && n < 8) {
+                    const int en = ctab[k];
+                    ++k;
+                    if (en != 0) {
+                        const float* sp = p.part + ((size_t)(en - 1) * NWG + w) * (MP * TN);
 #pragma unroll
-                for (int e = 0; e < NV; ++e) v[e] += t[e];
+                        for (int j = 0; j < 8; ++j)
+                            if (j == n) src[j] = sp;
+                        ++n;
+                    }
+                }
+                float t[8][NV];
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+#pragma unroll
+                    for (int e = 0; e < NV; ++e) t[j][e] = (j < n) ? __ldcg(src[j] + (e * SP + s) * TN + nl) : 0.0f;
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+#pragma unroll
+                    for (int e = 0; e < NV; ++e)
+                        if (j < n) v[e] += t[j][e];
             }
             if (tile < p.NT) {
                 const int n = tile * TN + nl;
@@ -581,18 +628,20 @@ __global__ void __launch_bounds__(tb_threads(NSUB), 1)
                     if (m < M) p.y[(size_t)m * N + n] = __float2half_rn(v[e] + b);
                 }
             }
-            // the counters go back to zero: the last of this CTA's compute warps to be done with a slot clears it
+            // the counters go back to zero: the last of this CTA's compute warps to be done with them clears them (plain
+            // stores, one lane per step owner; a returning atomic per contributor from one lane cost a round trip each)
             __syncwarp();
-            if (lane == 0) {
-                prev = -1;
-                for (int k = 0; k < KB; ++k) {
-                    const int cc = sg.cta_of((unsigned int)(rt * KB + k));
-                    if (cc == prev || cc == (int)blockIdx.x) continue;
-                    prev = cc;
-                    unsigned int* f = p.flags + cc * 2 + sg.slot_of((unsigned int)cc, rt);
-                    if (atomicAdd(f, 1u) == (unsigned int)(8 * NWG - 1)) atomicExch(f, 0u);
+            int old = 0;
+            if (lane == 0) old = atomicAdd(const_cast<int*>(done_cnt) + h, 1);
+            old = __shfl_sync(0xffffffffu, old, 0);
+            if (old == 4 * NWG - 1) {
+                for (int k2 = lane; k2 < KB; k2 += 32) {
+                    const int en = ctab[k2];
+                    if (en != 0 && en != self_ent)
+                        asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p.flags + (en - 1)), "r"(0u) : "memory");
                 }
             }
+            named_bar_sync(14, NWG * 128);         // the list may be overwritten for the next tile group
         }
     }
     // ------------------------------ teardown ------------------------------
@@ -651,7 +700,7 @@ bool linear_tcb_supported(const PackedW& w, int M) {
     if (w.G != 256 && w.G != 128) return false;
     if (M < 2 || M > 32) return false;
     if (w.G == 128 && M > 16) return false;                                      // tensor-memory columns
-    if (w.N % ts_tn(w.S) || w.K % 256) return false;
+    if (w.N % ts_tn(w.S) || w.K % 256 || w.K > 32768) return false;              // at most 128 k blocks (contributor lists)
     if (w.idx_bytes < 0 || w.idx_bytes > 2) return false;
     if (reinterpret_cast<uintptr_t>(w.coeff) & 15) return false;                 // bulk copies
     if (reinterpret_cast<uintptr_t>(w.bvr) & 15) return false;                   // tensor map base
