@@ -133,6 +133,106 @@ __global__ void __launch_bounds__(1024) allreduce_add_rmsnorm_kernel(
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// The receiving side of the pushed form: every rank's row-parallel decode GEMV has stored its partial result into slot
+// [call parity][rank] of THIS rank's receive area as 8-byte packets (two fp16 values | epoch << 32), so nothing is read
+// over NVLink here and no flag is exchanged: a thread polls its own packets of every rank until their epochs match
+// (bounded), adds them in rank order (the same bits on every rank and run), and finishes residual add + RMSNorm like
+// the kernel above.  A slot is overwritten two calls later, which a peer can only reach after this rank has pushed the
+// call in between, i.e. after this kernel has finished (stream order).
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ ulonglong2 ld_volatile_v2(const unsigned long long* p) {
+    ulonglong2 v;
+    asm volatile("ld.volatile.global.v2.u64 {%0, %1}, [%2];" : "=l"(v.x), "=l"(v.y) : "l"(p) : "memory");
+    return v;
+}
+
+__global__ void __launch_bounds__(1024) ll_reduce_add_rmsnorm_kernel(
+    const unsigned long long* __restrict__ recv,      // [2][world][rows_max][hidden / 2]
+    const int* __restrict__ step_ptr, int calls_per_step, int call_idx, int world, int rows_max, const __half* h_in,
+    const __half* __restrict__ weight, __half* h_out, __half* __restrict__ y, int hidden, float eps, unsigned int* status) {
+    __shared__ float red[32];
+    pdl_launch_dependents();
+    pdl_wait();                                    // the residual and the step counter belong to earlier kernels until now
+    const unsigned int epoch = (unsigned int)(*step_ptr) * (unsigned int)calls_per_step + (unsigned int)call_idx + 1u;
+    const size_t row = (size_t)blockIdx.x * hidden;
+    const int nvec = hidden / 8;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+        float acc[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = 0.0f;
+        for (int r0 = 0; r0 < world; r0 += 8) {
+            ulonglong2 a[8], b[8];
+            const long long t0 = clock64();
+            for (;;) {
+                // the packets of up to eight ranks are all requested before the first is looked at
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int r = (r0 + u < world) ? r0 + u : r0;
+                    const unsigned long long* src =
+                        recv + (((size_t)(call_idx & 1) * world + r) * rows_max + blockIdx.x) * (size_t)(hidden / 2) + (size_t)i * 4;
+                    a[u] = ld_volatile_v2(src);
+                    b[u] = ld_volatile_v2(src + 2);
+                }
+                bool done = true;
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+                    if (r0 + u < world)
+                        done = done && (unsigned int)(a[u].x >> 32) == epoch && (unsigned int)(a[u].y >> 32) == epoch &&
+                               (unsigned int)(b[u].x >> 32) == epoch && (unsigned int)(b[u].y >> 32) == epoch;
+                if (done) break;
+                if (clock64() - t0 > 600000000LL) {           // about a third of a second: a rank never delivered
+                    atomicExch(status, 1u);
+                    atomicExch(status + 1, 0x710u);
+                    break;
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                if (r0 + u < world) {
+                    const unsigned int w4[4] = {(unsigned int)a[u].x, (unsigned int)a[u].y, (unsigned int)b[u].x, (unsigned int)b[u].y};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w4[e]));
+                        acc[2 * e] += f.x, acc[2 * e + 1] += f.y;
+                    }
+                }
+            }
+        }
+        uint4 hv = *reinterpret_cast<const uint4*>(h_in + row + (size_t)i * 8);
+        __half2* ah = reinterpret_cast<__half2*>(&hv);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            ah[e] = __hadd2(ah[e], __floats2half2_rn(acc[2 * e], acc[2 * e + 1]));
+            const float2 f = __half22float2(ah[e]);
+            ss += f.x * f.x + f.y * f.y;
+        }
+        *reinterpret_cast<uint4*>(h_out + row + (size_t)i * 8) = hv;
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.0f;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) tot += red[w];
+    const float rs = rsqrtf(tot / (float)hidden + eps);
+    for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+        const uint4 hv = *reinterpret_cast<const uint4*>(h_out + row + (size_t)i * 8);    // written above by this thread
+        const uint4 wv = *reinterpret_cast<const uint4*>(weight + (size_t)i * 8);
+        const __half2* ah = reinterpret_cast<const __half2*>(&hv);
+        const __half2* wh = reinterpret_cast<const __half2*>(&wv);
+        uint4 o;
+        __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = __half22float2(ah[e]);
+            oh[e] = __hmul2(wh[e], __floats2half2_rn(f.x * rs, f.y * rs));
+        }
+        *reinterpret_cast<uint4*>(y + row + (size_t)i * 8) = o;
+    }
+}
+
 }  // namespace sbvr
 
 using namespace sbvr;
@@ -154,6 +254,26 @@ extern "C" int sbvr_allreduce_add_rmsnorm_f16(const void* peer_bufs_dev, const v
                              reinterpret_cast<const unsigned long long*>(peer_bufs_dev),
                              reinterpret_cast<const unsigned long long*>(peer_flags_dev), step_dev, calls_per_step, call_idx,
                              rank, world, buf_elems, reinterpret_cast<const __half*>(h_in),
+                             reinterpret_cast<const __half*>(weight), reinterpret_cast<__half*>(h_out),
+                             reinterpret_cast<__half*>(y), hidden, eps, ws->status));
+    return SBVR_OK;
+}
+
+extern "C" int sbvr_ll_reduce_add_rmsnorm_f16(const void* recv_local, const int* step_dev, int calls_per_step, int call_idx,
+                                               int world, int rows_max, const void* h_in, const void* weight, void* h_out,
+                                               void* y, int rows, int hidden, float eps, sbvr_workspace_t* ws,
+                                               sbvr_stream_t stream) {
+    if (!recv_local || !step_dev || !h_in || !weight || !h_out || !y || !ws) return SBVR_ERR_BAD_ARG;
+    if (world < 1 || world > AR_MAX_WORLD || rows < 1 || rows > rows_max || calls_per_step < 1 || call_idx < 0 ||
+        call_idx >= calls_per_step || (calls_per_step & 1))
+        return SBVR_ERR_BAD_ARG;
+    if (hidden < 8 || hidden % 8) return SBVR_ERR_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(recv_local) | reinterpret_cast<uintptr_t>(h_in) | reinterpret_cast<uintptr_t>(weight) |
+         reinterpret_cast<uintptr_t>(h_out) | reinterpret_cast<uintptr_t>(y)) & 15)
+        return SBVR_ERR_ALIGN;
+    SBVR_CUDA_TRY(launch_pdl(ll_reduce_add_rmsnorm_kernel, dim3(rows), dim3(hidden >= 8192 ? 1024 : 512), 0,
+                             reinterpret_cast<cudaStream_t>(stream), reinterpret_cast<const unsigned long long*>(recv_local),
+                             step_dev, calls_per_step, call_idx, world, rows_max, reinterpret_cast<const __half*>(h_in),
                              reinterpret_cast<const __half*>(weight), reinterpret_cast<__half*>(h_out),
                              reinterpret_cast<__half*>(y), hidden, eps, ws->status));
     return SBVR_OK;

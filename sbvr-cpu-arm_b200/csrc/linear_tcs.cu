@@ -71,6 +71,7 @@ struct TsParams {
     int pre_stages;               // stages requested before the activations are fetched
     int steps_bytes;              // bytes of the steps, rounded up to a multiple of 16
     int off_red, off_cache, off_ring, off_b;      // shared-memory carve-up; at off_b: [1 KB zeros][digits][1 KB zeros][steps]
+    PushDst push;                 // push.world > 0: the result goes to the ranks' receive areas as tagged packets, not to y
 };
 
 struct XqParams {
@@ -420,7 +421,32 @@ __global__ void __launch_bounds__(ts_threads(NSUB, M, KS), 1)
                     }
                 }
             }
-            if (fin) {
+            if (fin && p.push.world > 0) {
+                // Tensor parallel: (two fp16 outputs | epoch << 32) to slot [epoch parity][this rank] of every rank's receive
+                // area, one 8-byte store per peer and pair (M * TN is a multiple of 32: a warp's 32 values are valid together).
+                const unsigned int epoch = (unsigned int)(*p.push.step) * (unsigned int)p.push.calls_per_step +
+                                           (unsigned int)p.push.call_idx + 1u;
+                const size_t slot = ((size_t)(p.push.call_idx & 1) * p.push.world + p.push.rank) * p.push.rows_max;
+#pragma unroll
+                for (int e = 0; e < PER; ++e) {
+                    const int i = lane + 32 * e;
+                    if (i < M * TN) {
+                        const int m = i / TN, nl = i % TN;
+                        const float b = p.bias ? __half2float(p.bias[n0 + nl]) : 0.0f;
+                        const unsigned int h = __half_as_ushort(__float2half_rn(v[e] + b));
+                        const unsigned int hn = __shfl_down_sync(0xffffffffu, h, 1);
+                        if ((lane & 1) == 0) {
+                            const unsigned long long pk = (unsigned long long)(h | (hn << 16)) | ((unsigned long long)epoch << 32);
+                            const size_t at = (slot + m) * (size_t)(N / 2) + (size_t)((n0 + nl) >> 1);
+                            for (int r = 0; r < p.push.world; ++r)
+                                asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(
+                                                 reinterpret_cast<unsigned long long*>(p.push.peer_recv[r]) + at),
+                                             "l"(pk)
+                                             : "memory");
+                        }
+                    }
+                }
+            } else if (fin) {
 #pragma unroll
                 for (int e = 0; e < PER; ++e) {
                     const int i = lane + 32 * e;
@@ -920,7 +946,7 @@ static int ts_launch_g(const CUtensorMap& tm, const TsParams& p, int G, int M, i
 // carve them differently.
 int launch_linear_tcs(const __half* x, const PackedW& w, const __half* bias, __half* y, int M, int device,
                       unsigned int* status, unsigned long long* xchg, char* scratch, size_t scratch_bytes, cudaStream_t st,
-                      const XOp* xop) {
+                      const XOp* xop, const PushDst* push) {
     if (!linear_tcs_supported(w, M)) return SBVR_ERR_UNSUPPORTED;
     if (!status || !xchg || !scratch) return SBVR_ERR_WORKSPACE;
     if (reinterpret_cast<uintptr_t>(x) & 15) return SBVR_ERR_ALIGN;      // x is fetched 16 bytes at a time
@@ -974,6 +1000,14 @@ int launch_linear_tcs(const __half* x, const PackedW& w, const __half* bias, __h
     p.steps_bytes = pl.steps_bytes;
     p.pre_stages = pl.stages < 3 ? pl.stages : 3;
     p.off_red = pl.off_red, p.off_cache = pl.off_cache, p.off_ring = pl.off_ring, p.off_b = pl.off_b;
+    if (push) {
+        if (!push->peer_recv || !push->step || push->world < 1 || push->rank < 0 || push->rank >= push->world || M > push->rows_max ||
+            (w.N & 1))
+            return SBVR_ERR_BAD_ARG;
+        p.push = *push;
+    } else {
+        p.push = PushDst{nullptr, nullptr, 0, 0, 0, 0, 0};
+    }
     switch (w.S) {
         case 2: return ts_launch_g<2>(tm, p, w.G, M, w.idx_bytes, pl.KS, pl.grid, pl.smem, st);
         case 3: return ts_launch_g<3>(tm, p, w.G, M, w.idx_bytes, pl.KS, pl.grid, pl.smem, st);

@@ -1,9 +1,13 @@
-"""Symmetric-memory buffers and the fused all-reduce + add + RMSNorm call of the tensor-parallel decode step.
+"""Symmetric-memory buffers and the fused all-reduce + add + RMSNorm calls of the tensor-parallel decode step.
 
 Every rank allocates the same block with torch's symmetric-memory allocator and exchanges the mappings once
-(`rendezvous`); afterwards each rank holds plain device pointers to all peers' blocks.  The row-parallel linears
-write their partial outputs straight into the local block; `sbvr_allreduce_add_rmsnorm_f16` then reads all peers'
-partials over NVLink (ordinary loads) and finishes the layer's residual add and RMSNorm in the same launch.
+(`rendezvous`); afterwards each rank holds plain device pointers to all peers' blocks.  Two forms:
+
+* up to four rows (decode): the row-parallel linear's own epilogue stores its result as epoch-tagged 8-byte packets into
+  every rank's receive area (`sbvr_linear_push_f16`), and `sbvr_ll_reduce_add_rmsnorm_f16` adds the packets that have
+  arrived in the local area and finishes the residual add and RMSNorm: one NVLink crossing, no flags;
+* more rows: the linears write their partial outputs into the local block and `sbvr_allreduce_add_rmsnorm_f16` reads all
+  peers' partials over NVLink (ordinary loads) after a flag exchange.
 """
 from __future__ import annotations
 
@@ -28,7 +32,10 @@ class SymmetricAllReduce:
         self.max_rows, self.hidden, self.calls_per_step = max_rows, hidden, calls_per_step
         self.buf_elems = max_rows * hidden
         data_bytes = 2 * self.buf_elems * 2
-        self.block = symm.empty(data_bytes + self.FLAG_BYTES, dtype=torch.uint8, device=device)
+        self.push_rows = min(4, max_rows)           # the pushed form exists for the decode GEMV (up to four rows)
+        recv_off = data_bytes + self.FLAG_BYTES
+        recv_bytes = 2 * self.world * self.push_rows * (hidden // 2) * 8
+        self.block = symm.empty(recv_off + recv_bytes, dtype=torch.uint8, device=device)
         self.block.zero_()
         torch.cuda.synchronize(device)
         self.handle = symm.rendezvous(self.block, group)
@@ -36,6 +43,8 @@ class SymmetricAllReduce:
         ptrs = [int(p) for p in self.handle.buffer_ptrs]
         self.bufs_dev = torch.tensor(ptrs, dtype=torch.int64, device=device)
         self.flags_dev = torch.tensor([p + data_bytes for p in ptrs], dtype=torch.int64, device=device)
+        self.recv_dev = torch.tensor([p + recv_off for p in ptrs], dtype=torch.int64, device=device)
+        self.recv_local = ptrs[self.rank] + recv_off
         self.step = torch.zeros(1, dtype=torch.int32, device=device)
         self.local = self.block[:data_bytes].view(torch.float16).view(2, max_rows, hidden)
 
@@ -49,6 +58,36 @@ class SymmetricAllReduce:
             self.bufs_dev.data_ptr(), self.flags_dev.data_ptr(), self.step.data_ptr(), self.calls_per_step, call_idx,
             self.rank, self.world, self.buf_elems, h.data_ptr(), weight.data_ptr(), h.data_ptr(), y.data_ptr(), rows,
             self.hidden, eps, ws.handle, stream), "sbvr_allreduce_add_rmsnorm_f16")
+
+    def push_linear(self, call_idx: int, x_op: int, x: torch.Tensor, w, rows: int, bias=None) -> bool:
+        """The row-parallel linear of call `call_idx`, its result pushed to every rank's receive area.  False (nothing
+        launched) where the decode GEMV does not apply: the caller then uses partial_out + reduce_add_rmsnorm."""
+        from sbvr.core import _cuda_index, _ptr
+        if rows > self.push_rows or not x.is_contiguous() or w.out_features != self.hidden:
+            return False
+        Kp = w.in_features_padded
+        if int(w.original_data_shape[-1]) != Kp:
+            return False
+        b, ix, ib, c, C = w._abi_args()
+        di = _cuda_index(w.bvr.device)
+        with torch.cuda.device(di):
+            st = torch.cuda.current_stream().cuda_stream
+            ws = _lib.workspace(di, st)
+            rc = _lib.lib.sbvr_linear_push_f16(x_op, x.data_ptr(), None, None, None, 0.0, b, ix, ib, c, C, _ptr(bias),
+                                               self.recv_dev.data_ptr(), self.step.data_ptr(), self.calls_per_step, call_idx,
+                                               self.rank, self.world, self.push_rows, rows, self.hidden, Kp, w.num_sums,
+                                               w.bvr_len, ws.handle, st)
+        if rc == -7:
+            return False
+        _lib.check(rc, "sbvr_linear_push_f16")
+        return True
+
+    def ll_reduce_add_rmsnorm(self, call_idx: int, h: torch.Tensor, weight: torch.Tensor, y: torch.Tensor, rows: int,
+                              eps: float, ws, stream: int):
+        _lib.check(_lib.lib.sbvr_ll_reduce_add_rmsnorm_f16(
+            self.recv_local, self.step.data_ptr(), self.calls_per_step, call_idx, self.world, self.push_rows,
+            h.data_ptr(), weight.data_ptr(), h.data_ptr(), y.data_ptr(), rows, self.hidden, eps, ws.handle, stream),
+            "sbvr_ll_reduce_add_rmsnorm_f16")
 
     def end_step(self):
         self.step.add_(1)

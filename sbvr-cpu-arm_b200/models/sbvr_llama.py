@@ -24,7 +24,7 @@ import torch
 
 import sbvr as _sbvr
 from sbvr import _lib
-from sbvr.core import XOP_ADD_RMSNORM, XOP_SILU_MUL, linear_fused
+from sbvr.core import XOP_ADD_RMSNORM, XOP_NONE, XOP_SILU_MUL, linear_fused
 from sbvr.core import linear as sbvr_linear
 from sbvr.core import sbvr as sbvr_tensor
 
@@ -350,21 +350,31 @@ class SBVRLlamaForCausalLM(torch.nn.Module):
                                         b.positions.data_ptr(), b.ao.data_ptr(), att_scratch, T, tokens_per_seq,
                                         self.n_heads, self.n_kv, c.head_dim, self.max_ctx, scale, nsplit, st), "attention")
             if comm is not None:
-                layer.o_proj(b.ao, out=comm.partial_out(2 * li, T))
-                comm.reduce_add_rmsnorm(2 * li, hc, layer.post_attention_layernorm_weight, b.xn, T, eps, ws, st)
+                # decode: the o projection pushes its result into every rank's receive area (no separate all-reduce)
+                if fuse and isinstance(layer.o_proj, SBVRLinear) and comm.push_linear(
+                        2 * li, XOP_NONE, b.ao, layer.o_proj.weight, T, bias=layer.o_proj.bias):
+                    comm.ll_reduce_add_rmsnorm(2 * li, hc, layer.post_attention_layernorm_weight, b.xn, T, eps, ws, st)
+                else:
+                    layer.o_proj(b.ao, out=comm.partial_out(2 * li, T))
+                    comm.reduce_add_rmsnorm(2 * li, hc, layer.post_attention_layernorm_weight, b.xn, T, eps, ws, st)
                 layer.gate_up_proj(b.xn, out=b.gu)
             else:
                 layer.o_proj(b.ao, out=b.o)
                 self._all_reduce(b.o)
                 norm_linear(layer.gate_up_proj, b.o, layer.post_attention_layernorm_weight, b.gu)
             down_out = comm.partial_out(2 * li + 1, T) if comm is not None else b.down
-            if not (fuse and isinstance(layer.down_proj, SBVRLinear) and
-                    linear_fused(XOP_SILU_MUL, b.gu, layer.down_proj.weight, down_out, bias=layer.down_proj.bias)):
+            pushed = (comm is not None and fuse and isinstance(layer.down_proj, SBVRLinear) and
+                      comm.push_linear(2 * li + 1, XOP_SILU_MUL, b.gu, layer.down_proj.weight, T, bias=layer.down_proj.bias))
+            if not pushed and not (fuse and isinstance(layer.down_proj, SBVRLinear) and
+                                   linear_fused(XOP_SILU_MUL, b.gu, layer.down_proj.weight, down_out, bias=layer.down_proj.bias)):
                 ck(L.sbvr_silu_mul_f16(b.gu.data_ptr(), b.act.data_ptr(), T, self.inter, st), "silu_mul")
                 layer.down_proj(b.act, out=down_out)
             if comm is not None:
                 nw = self.layers[li + 1].input_layernorm_weight if li + 1 < n_layers else self.norm_weight
-                comm.reduce_add_rmsnorm(2 * li + 1, hc, nw, b.xn, T, eps, ws, st)
+                if pushed:
+                    comm.ll_reduce_add_rmsnorm(2 * li + 1, hc, nw, b.xn, T, eps, ws, st)
+                else:
+                    comm.reduce_add_rmsnorm(2 * li + 1, hc, nw, b.xn, T, eps, ws, st)
                 delta, normed = None, True
             else:
                 self._all_reduce(b.down)

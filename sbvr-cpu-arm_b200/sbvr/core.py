@@ -326,7 +326,7 @@ def linear(x: torch.Tensor, w: sbvr, bias: Optional[torch.Tensor] = None, algo: 
     return y.view(*lead, N)
 
 
-XOP_SILU_MUL, XOP_ADD_RMSNORM = 1, 2
+XOP_NONE, XOP_SILU_MUL, XOP_ADD_RMSNORM = 0, 1, 2
 
 
 @torch.inference_mode()
