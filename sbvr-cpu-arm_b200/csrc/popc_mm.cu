@@ -60,29 +60,41 @@ __global__ void __launch_bounds__(PM_THREADS) popc_mm_kernel(const uint32_t* __r
     float acc[PM_MT];
 #pragma unroll
     for (int m = 0; m < PM_MT; ++m) acc[m] = 0.0f;
-    for (int g = g0; g < g1; ++g) {
-        uint32_t rw[8];
+    // Two groups per iteration: their sixteen packed words and two coefficients are requested before the first popcount
+    // (with one group in flight per warp the weight stream was latency-bound).
+    for (int g = g0; g < g1; g += 2) {
+        uint32_t rw[2][8];
+        float cr[2];
 #pragma unroll
-        for (int kw = 0; kw < 8; ++kw) rw[kw] = live ? __ldcs(r_bvr + ((size_t)(g * 8 + kw) * N + n) * RS + b) : 0u;
-        float cr = 0.0f;
-        if (live) {
-            const size_t e = (size_t)g * N + n;
-            const size_t line = (r_idx_bytes == 1) ? reinterpret_cast<const uint8_t*>(r_idx)[e]
-                                                   : reinterpret_cast<const uint16_t*>(r_idx)[e];
-            cr = __half2float(r_cache[line * RS + b]);
+        for (int u = 0; u < 2; ++u) {
+            const bool on = live && (g + u < g1);
+#pragma unroll
+            for (int kw = 0; kw < 8; ++kw) rw[u][kw] = on ? __ldcs(r_bvr + ((size_t)((g + u) * 8 + kw) * N + n) * RS + b) : 0u;
+            cr[u] = 0.0f;
+            if (on) {
+                const size_t e = (size_t)(g + u) * N + n;
+                const size_t line = (r_idx_bytes == 1) ? reinterpret_cast<const uint8_t*>(r_idx)[e]
+                                                       : reinterpret_cast<const uint16_t*>(r_idx)[e];
+                cr[u] = __half2float(r_cache[line * RS + b]);
+            }
         }
 #pragma unroll
-        for (int m = 0; m < PM_MT; ++m) {
-            if (m < mt) {
-                float s = 0.0f;
+        for (int u = 0; u < 2; ++u) {
+            if (g + u < g1) {
 #pragma unroll
-                for (int a = 0; a < LS; ++a) {
-                    int cnt = 0;
+                for (int m = 0; m < PM_MT; ++m) {
+                    if (m < mt) {
+                        float s = 0.0f;
 #pragma unroll
-                    for (int kw = 0; kw < 8; ++kw) cnt += __popc(lw[((g * 8 + kw) * PM_MT + m) * LS + a] & rw[kw]);
-                    s += lc[(g * PM_MT + m) * LS + a] * (float)cnt;
+                        for (int a = 0; a < LS; ++a) {
+                            int cnt = 0;
+#pragma unroll
+                            for (int kw = 0; kw < 8; ++kw) cnt += __popc(lw[(((g + u) * 8 + kw) * PM_MT + m) * LS + a] & rw[u][kw]);
+                            s += lc[((g + u) * PM_MT + m) * LS + a] * (float)cnt;
+                        }
+                        acc[m] += cr[u] * s;
+                    }
                 }
-                acc[m] += cr * s;
             }
         }
     }
