@@ -474,7 +474,7 @@ def small_m_and_prefill(torch, dev, stream):
             r["algo"] = algo
         return r
 
-    sweep, prefill, rowdeq, direct128, others = [], [], [], [], []
+    sweep, prefill, rowdeq, direct128, others, batch = [], [], [], [], [], []
     for N, K in shapes:
         for s in (4, 3, 2):
             ncopy = int(2 * 126e6 / (N * K * s / 8)) + 2
@@ -485,6 +485,15 @@ def small_m_and_prefill(torch, dev, stream):
                 us = median_graph_time_us(torch, stream, [(lambda w=w, o=o: sbvr.linear(x, w, None, out=o)) for w, o in zip(ws_, outs)])
                 sweep.append(row(N, K, M, s, G, us, IDXB))
             if s == 4:
+                # the two kernels for small batches side by side, whatever the automatic choice is
+                for M in (16, 32):
+                    x = torch.randn((M, K), device=dev, generator=gen).half()
+                    outs = [torch.empty((M, N), dtype=torch.float16, device=dev) for _ in range(ncopy)]
+                    for algo, name in ((3, "fp16 GEMM with in-kernel dequantisation (linear_gemm_kernel)"),
+                                       (4, "FP4 digits with block scale factors (xq8_kernel + linear_tcb_kernel)")):
+                        us = median_graph_time_us(torch, stream, [(lambda w=w, o=o: sbvr.linear(x, w, None, algo=algo, out=o))
+                                                                  for w, o in zip(ws_, outs)], repeats=3)
+                        batch.append(dict(row(N, K, M, 4, G, us, IDXB, algo=algo), kernel=name))
                 x = torch.randn((1, K), device=dev, generator=gen).half()
                 outs = [torch.empty((1, N), dtype=torch.float16, device=dev) for _ in range(ncopy)]
                 us = median_graph_time_us(torch, stream, [(lambda w=w, o=o: sbvr.linear(x, w, None, algo=1, out=o)) for w, o in zip(ws_, outs)], reps=2, repeats=3)
@@ -555,6 +564,7 @@ def small_m_and_prefill(torch, dev, stream):
            "relative_mse": round(rel, 5), **we.encoder_stats}
     return {"small_m_sweep": {"G": G, "index": "u16 codebook C=4096", "rows": sweep},
             "group128_direct": {"rows": direct128},
+            "small_batch_kernels": {"rows": batch},
             "other_formulations_m1": others, "prefill_gemm": prefill,
             "row_deq_transposed_layout": {"S": S, "G": G, "rows": rowdeq}, "encoder": enc}
 
@@ -601,12 +611,21 @@ def llama_decode(torch, dev, dist, world, preset, batch, prompt, new_tokens):
     if dist:
         exchange = "NCCL all-reduce"
         fused_ms = None
-        if m.enable_fused_allreduce(16):               # same decode with the fused peer-memory all-reduce kernel
+        pull_ms = None
+        if m.enable_fused_allreduce(16):               # same decode with the exchanges over symmetric peer memory
             nccl_ms = ms
-            fused_ms = timed_decode()
-            if fused_ms <= nccl_ms:                    # the faster exchange is the one reported as tokens_per_s
+            m.set_pushed_allreduce(False)              # one-shot all-reduce kernel: flags, then loads over NVLink
+            pull_ms = timed_decode()
+            fused_ms, fused_name = pull_ms, "fused one-shot all-reduce + add + RMSNorm over symmetric memory (peer loads)"
+            if batch <= 4:                             # decode GEMV: results pushed by its epilogue as tagged packets
+                m.set_pushed_allreduce(True)
+                push_ms = timed_decode()
+                if push_ms <= fused_ms:
+                    fused_ms, fused_name = push_ms, ("row-parallel GEMV pushes epoch-tagged packets to every rank, packet "
+                                                     "reduce + add + RMSNorm on the receiver (no flags, no peer loads)")
+            if fused_ms <= nccl_ms:                    # the fastest exchange is the one reported as tokens_per_s
                 ms = fused_ms
-                exchange = "fused one-shot all-reduce + add + RMSNorm over symmetric memory"
+                exchange = fused_name
         t = torch.tensor([prefill_ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         prefill_ms = float(t[0].item())
@@ -621,6 +640,9 @@ def llama_decode(torch, dev, dist, world, preset, batch, prompt, new_tokens):
     if nccl_ms is not None:
         res["tokens_per_s_nccl"] = round(batch * new_tokens / nccl_ms * 1e3, 1)
         res["tokens_per_s_fused_allreduce"] = round(batch * new_tokens / fused_ms * 1e3, 1)
+        res["tokens_per_s_one_shot_peer_loads"] = round(batch * new_tokens / pull_ms * 1e3, 1)
+        if batch <= 4:
+            res["tokens_per_s_pushed_packets"] = round(batch * new_tokens / push_ms * 1e3, 1)
     del m
     torch.cuda.empty_cache()
     return res

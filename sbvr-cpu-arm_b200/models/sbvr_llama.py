@@ -189,6 +189,7 @@ class SBVRLlamaForCausalLM(torch.nn.Module):
         self._stream = None
         self._comm = None
         self.fuse_glue = True                      # fold norm / SiLU into the decode linears where the kernel allows
+        self.pushed_allreduce = True               # tensor-parallel decode: results pushed to the peers by the GEMV itself
         self._argmax_scratch = torch.empty(256, dtype=torch.float32, device=self.device)
 
     # ------------------------------------------------------------------ weights
@@ -244,6 +245,12 @@ class SBVRLlamaForCausalLM(torch.nn.Module):
             self._comm = None
         self._graph = None
         return self._comm is not None
+
+    def set_pushed_allreduce(self, on: bool) -> None:
+        """Decode (up to four rows): whether the row-parallel linears push their results into the ranks' receive areas
+        (on by default) or write partials that the one-shot all-reduce kernel then reads over NVLink."""
+        self.pushed_allreduce = bool(on)
+        self._graph = None
 
     def _alloc_cache(self):
         c = self.config
@@ -351,7 +358,7 @@ class SBVRLlamaForCausalLM(torch.nn.Module):
                                         self.n_heads, self.n_kv, c.head_dim, self.max_ctx, scale, nsplit, st), "attention")
             if comm is not None:
                 # decode: the o projection pushes its result into every rank's receive area (no separate all-reduce)
-                if fuse and isinstance(layer.o_proj, SBVRLinear) and comm.push_linear(
+                if fuse and self.pushed_allreduce and isinstance(layer.o_proj, SBVRLinear) and comm.push_linear(
                         2 * li, XOP_NONE, b.ao, layer.o_proj.weight, T, bias=layer.o_proj.bias):
                     comm.ll_reduce_add_rmsnorm(2 * li, hc, layer.post_attention_layernorm_weight, b.xn, T, eps, ws, st)
                 else:
@@ -363,7 +370,7 @@ class SBVRLlamaForCausalLM(torch.nn.Module):
                 self._all_reduce(b.o)
                 norm_linear(layer.gate_up_proj, b.o, layer.post_attention_layernorm_weight, b.gu)
             down_out = comm.partial_out(2 * li + 1, T) if comm is not None else b.down
-            pushed = (comm is not None and fuse and isinstance(layer.down_proj, SBVRLinear) and
+            pushed = (comm is not None and fuse and self.pushed_allreduce and isinstance(layer.down_proj, SBVRLinear) and
                       comm.push_linear(2 * li + 1, XOP_SILU_MUL, b.gu, layer.down_proj.weight, T, bias=layer.down_proj.bias))
             if not pushed and not (fuse and isinstance(layer.down_proj, SBVRLinear) and
                                    linear_fused(XOP_SILU_MUL, b.gu, layer.down_proj.weight, down_out, bias=layer.down_proj.bias)):
