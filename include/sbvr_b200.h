@@ -251,20 +251,26 @@ SBVR_API int sbvr_allreduce_add_rmsnorm_f16(const void* peer_bufs_dev, const voi
 /* ---- tensor parallel, decode: the all-reduce folded into the row-parallel GEMV and its consumer ----------------
  * sbvr_linear_push_f16 is sbvr_linear_fused_f16 (x_op may also be SBVR_XOP_NONE) whose result does not go to y: the
  * decode GEMV's epilogue stores every pair of fp16 outputs together with the call's epoch as one 8-byte packet into
- * slot [call_idx & 1][rank] of EVERY rank's receive area (peer_recv_dev: device array of `world` 64-bit base
- * addresses, this rank's own included; an area is uint64 [2][world][rows_max][N / 2], zero before the first call),
- * with plain stores over NVLink.  sbvr_ll_reduce_add_rmsnorm_f16 is the other end: it reads only THIS rank's area,
+ * slot [call_idx & 1][rank] of EVERY rank's receive area (this rank's own included; an area is uint64
+ * [2][world][rows_max][N / 2], zero before the first call), with plain stores over NVLink.  Where to push is described
+ * by an sbvr_push_desc_t in DEVICE memory (written once per call index by the caller; the kernel reads it, the host
+ * side of the library does not).  sbvr_ll_reduce_add_rmsnorm_f16 is the other end: it reads only THIS rank's area,
  * waits (bounded, reported through the workspace status word) until the packets of all ranks carry the epoch, adds them
  * in rank order in fp32 and finishes h_out = h_in + fp16(sum), y = RMSNorm(h_out) * weight.  No flag exchange, no load
- * over NVLink, no multicast.  Epoch = *step_dev * calls_per_step + call_idx + 1 as for the one-shot form; both ends of
- * a call must be given the same step_dev value, calls_per_step (even) and call_idx.  M <= 4 (decode GEMV only): returns
+ * over NVLink, no multicast.  Epoch = *step * calls_per_step + call_idx + 1 as for the one-shot form; both ends of a call
+ * must be given the same step counter, calls_per_step (even) and call_idx.  M <= 4, G = 256 (decode GEMV only): returns
  * SBVR_ERR_UNSUPPORTED otherwise, and the caller uses sbvr_allreduce_add_rmsnorm_f16 or NCCL.
  * No counterpart in the reference (it has no tensor-parallel path); the pair replaces the row-parallel linear's store,
  * ncclAllReduce, and the add + LlamaRMSNorm of models/sbvr_llama.py:118-123, :395-406. */
+typedef struct sbvr_push_desc {
+    unsigned long long peer_recv[16];   /* base address of every rank's receive area (entries 0 .. world-1) */
+    const int* step;                    /* device int32: decode step counter, bumped once per step by the caller */
+    int calls_per_step, call_idx, rank, world, rows_max;
+    int reserved;
+} sbvr_push_desc_t;
 SBVR_API int sbvr_linear_push_f16(int x_op, const void* x, const void* delta, const void* norm_weight, void* h_out, float eps,
                                   const uint32_t* bvr, const void* coeff_idx, int idx_bytes, const void* coeff, int C,
-                                  const void* bias, const void* peer_recv_dev, const int* step_dev, int calls_per_step,
-                                  int call_idx, int rank, int world, int rows_max, int M, int N, int K, int S, int G,
+                                  const void* bias, const sbvr_push_desc_t* push_desc_dev, int M, int N, int K, int S, int G,
                                   sbvr_workspace_t* ws, sbvr_stream_t stream);
 SBVR_API int sbvr_ll_reduce_add_rmsnorm_f16(const void* recv_local, const int* step_dev, int calls_per_step, int call_idx,
                                             int world, int rows_max, const void* h_in, const void* weight, void* h_out,

@@ -253,36 +253,28 @@ int sbvr_linear_fused_f16(int x_op, const void* x, const void* delta, const void
 
 int sbvr_linear_push_f16(int x_op, const void* x, const void* delta, const void* norm_weight, void* h_out, float eps,
                          const uint32_t* bvr, const void* coeff_idx, int idx_bytes, const void* coeff, int C,
-                         const void* bias, const void* peer_recv_dev, const int* step_dev, int calls_per_step,
-                         int call_idx, int rank, int world, int rows_max, int M, int N, int K, int S, int G,
+                         const void* bias, const sbvr_push_desc_t* push_desc_dev, int M, int N, int K, int S, int G,
                          sbvr_workspace_t* ws, sbvr_stream_t stream) {
     PackedW w;
     int rc = make_packed(&w, bvr, coeff_idx, idx_bytes, coeff, C, N, K, S, G);
     if (rc) return rc;
-    if (!x || !peer_recv_dev || !step_dev || M < 1) return SBVR_ERR_BAD_ARG;
+    if (!x || !push_desc_dev || M < 1) return SBVR_ERR_BAD_ARG;
     if (x_op != SBVR_XOP_NONE && x_op != SBVR_XOP_SILU_MUL && x_op != SBVR_XOP_ADD_RMSNORM) return SBVR_ERR_BAD_ARG;
-    if (world < 1 || world > 16 || rank < 0 || rank >= world || rows_max < M || calls_per_step < 1 || call_idx < 0 ||
-        call_idx >= calls_per_step || (calls_per_step & 1))
-        return SBVR_ERR_BAD_ARG;
-    if (reinterpret_cast<uintptr_t>(x) & 15) return SBVR_ERR_ALIGN;
+    if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(push_desc_dev) & 7)) return SBVR_ERR_ALIGN;
     DeviceInfo di;
     if (!ws) return SBVR_ERR_WORKSPACE;
     rc = device_info(ws->device, &di);
     if (rc) return rc;
     if (di.cc_major != 10) return SBVR_ERR_UNSUPPORTED;
-    if (!linear_tcs_supported(w, M)) return SBVR_ERR_UNSUPPORTED;
+    if (G != 256 || !linear_tcs_supported(w, M)) return SBVR_ERR_UNSUPPORTED;
     if (linear_tcs_workspace_bytes(w, M, di.sm_count) > ws->dyn_bytes) return SBVR_ERR_WORKSPACE;
     XOp xop;
     xop.op = x_op;
     xop.delta = reinterpret_cast<const __half*>(delta), xop.norm_w = reinterpret_cast<const __half*>(norm_weight);
     xop.h_out = reinterpret_cast<__half*>(h_out), xop.eps = eps;
-    PushDst pd;
-    pd.peer_recv = reinterpret_cast<const unsigned long long*>(peer_recv_dev);
-    pd.step = step_dev;
-    pd.calls_per_step = calls_per_step, pd.call_idx = call_idx, pd.rank = rank, pd.world = world, pd.rows_max = rows_max;
     return launch_linear_tcs(reinterpret_cast<const __half*>(x), w, reinterpret_cast<const __half*>(bias), nullptr, M,
                              ws->device, ws->status, ws->xchg, ws->dyn, ws->dyn_bytes, reinterpret_cast<cudaStream_t>(stream),
-                             x_op == SBVR_XOP_NONE ? nullptr : &xop, &pd);
+                             x_op == SBVR_XOP_NONE ? nullptr : &xop, push_desc_dev);
 }
 
 int sbvr_linear_f16_host(const void* x_host, const uint32_t* bvr, const void* coeff_idx, int idx_bytes,

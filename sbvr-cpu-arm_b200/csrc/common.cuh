@@ -113,14 +113,8 @@ struct XOp {
     __half* h_out;           // ADD_RMSNORM: x + delta is stored here (may be NULL; must not be x)
     float eps;
 };
-// Where a row-parallel linear of a tensor-parallel model sends its result (decode GEMV only): instead of y, every pair of
-// fp16 outputs goes, with the call's epoch beside it, as one 8-byte packet into slot [call parity][rank] of EVERY rank's
-// receive area (plain stores to peer memory), where sbvr_ll_reduce_add_rmsnorm_f16 collects them.
-struct PushDst {
-    const unsigned long long* peer_recv;   // device array [world]: base address of every rank's receive area
-    const int* step;                       // device: decode step counter
-    int calls_per_step, call_idx, rank, world, rows_max;
-};
+// The decode GEMV can push its result to the ranks of a tensor-parallel model instead of storing y: `push` is an
+// sbvr_push_desc_t in device memory (include/sbvr_b200.h), read by the kernel only.
 // The decode GEMV (linear_tcs.cu): FP4 tensor-core dot products, weights through TMA, work split by 256-k steps.
 // The caller hands it its scratch: a status word pair, the zeroed exchange slots (SBVR_WS_XCHG_BYTES) and
 // `scratch_bytes` >= linear_tcs_workspace_bytes() of 256-byte aligned memory.
@@ -128,7 +122,7 @@ bool linear_tcs_supported(const PackedW& w, int M);
 size_t linear_tcs_workspace_bytes(const PackedW& w, int M, int sm_count);
 int launch_linear_tcs(const __half* x, const PackedW& w, const __half* bias, __half* y, int M, int device,
                       unsigned int* status, unsigned long long* xchg, char* scratch, size_t scratch_bytes, cudaStream_t st,
-                      const XOp* xop = nullptr, const PushDst* push = nullptr);
+                      const XOp* xop = nullptr, const sbvr_push_desc_t* push = nullptr);
 // The small-batch kernel (linear_tcb.cu), 2 .. 32 activation rows: same scratch rules; it uses the first words of the
 // exchange region as arrival counters and leaves them zero.
 bool linear_tcb_supported(const PackedW& w, int M);

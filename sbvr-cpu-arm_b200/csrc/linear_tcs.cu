@@ -64,14 +64,13 @@ struct TsParams {
     const void* idx;
     const __half* coeff;
     const __half* bias;
-    __half* y;
+    __half* y;                    // the pushing form of the kernel finds an sbvr_push_desc_t (device memory) here instead
     unsigned int* status;
     unsigned long long* xchg;     // [grid][2][M * TN] (fp32 sum | tag << 32) of the shared segments; all zero between calls
     int N, K, KB, NT, C, cache_in_smem, stages;
     int pre_stages;               // stages requested before the activations are fetched
     int steps_bytes;              // bytes of the steps, rounded up to a multiple of 16
     int off_red, off_cache, off_ring, off_b;      // shared-memory carve-up; at off_b: [1 KB zeros][digits][1 KB zeros][steps]
-    PushDst push;                 // push.world > 0: the result goes to the ranks' receive areas as tagged packets, not to y
 };
 
 struct XqParams {
@@ -177,7 +176,7 @@ __global__ void __launch_bounds__(512) xquant_kernel(const XqParams p) {
 // ---------------------------------------------------------------------------------------------
 // the product
 // ---------------------------------------------------------------------------------------------
-template <int S, int NSUB, int M, int IDXB, int KS>
+template <int S, int NSUB, int M, int IDXB, int KS, bool PUSH>
 __global__ void __launch_bounds__(ts_threads(NSUB, M, KS), 1)
     linear_tcs_kernel(const __grid_constant__ CUtensorMap tmap, const TsParams p) {
     static_assert(KS == 1 || (KS == 2 && NSUB == 1 && M == 1), "two blocks per step: one activation row, one group per block");
@@ -421,12 +420,13 @@ __global__ void __launch_bounds__(ts_threads(NSUB, M, KS), 1)
                     }
                 }
             }
-            if (fin && p.push.world > 0) {
+            if (PUSH && fin) {
                 // Tensor parallel: (two fp16 outputs | epoch << 32) to slot [epoch parity][this rank] of every rank's receive
                 // area, one 8-byte store per peer and pair (M * TN is a multiple of 32: a warp's 32 values are valid together).
-                const unsigned int epoch = (unsigned int)(*p.push.step) * (unsigned int)p.push.calls_per_step +
-                                           (unsigned int)p.push.call_idx + 1u;
-                const size_t slot = ((size_t)(p.push.call_idx & 1) * p.push.world + p.push.rank) * p.push.rows_max;
+                const sbvr_push_desc_t* pd = reinterpret_cast<const sbvr_push_desc_t*>(p.y);
+                const int world = pd->world;
+                const unsigned int epoch = (unsigned int)(*pd->step) * (unsigned int)pd->calls_per_step + (unsigned int)pd->call_idx + 1u;
+                const size_t slot = ((size_t)(pd->call_idx & 1) * world + pd->rank) * pd->rows_max;
 #pragma unroll
                 for (int e = 0; e < PER; ++e) {
                     const int i = lane + 32 * e;
@@ -438,15 +438,15 @@ __global__ void __launch_bounds__(ts_threads(NSUB, M, KS), 1)
                         if ((lane & 1) == 0) {
                             const unsigned long long pk = (unsigned long long)(h | (hn << 16)) | ((unsigned long long)epoch << 32);
                             const size_t at = (slot + m) * (size_t)(N / 2) + (size_t)((n0 + nl) >> 1);
-                            for (int r = 0; r < p.push.world; ++r)
+                            for (int r = 0; r < world; ++r)
                                 asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(
-                                                 reinterpret_cast<unsigned long long*>(p.push.peer_recv[r]) + at),
+                                                 reinterpret_cast<unsigned long long*>(pd->peer_recv[r]) + at),
                                              "l"(pk)
                                              : "memory");
                         }
                     }
                 }
-            } else if (fin) {
+            } else if (!PUSH && fin) {
 #pragma unroll
                 for (int e = 0; e < PER; ++e) {
                     const int i = lane + 32 * e;
@@ -898,47 +898,53 @@ int ts_tensor_map(const PackedW& w, int KS, CUtensorMap* out) {
     return SBVR_OK;
 }
 
-template <int S, int NSUB, int M, int IDXB, int KS>
+template <int S, int NSUB, int M, int IDXB, int KS, bool PUSH>
 static int ts_launch_inst(const CUtensorMap& tm, const TsParams& p, int grid, int smem, cudaStream_t st) {
     static SmemOnce once;
-    const int rc = set_max_smem_once(once, linear_tcs_kernel<S, NSUB, M, IDXB, KS>, 227 * 1024);
+    const int rc = set_max_smem_once(once, linear_tcs_kernel<S, NSUB, M, IDXB, KS, PUSH>, 227 * 1024);
     if (rc) return rc;
-    SBVR_CUDA_TRY(launch_pdl(linear_tcs_kernel<S, NSUB, M, IDXB, KS>, dim3(grid), dim3(ts_threads(NSUB, M, KS)), (size_t)smem,
-                             st, tm, p));
+    SBVR_CUDA_TRY(launch_pdl(linear_tcs_kernel<S, NSUB, M, IDXB, KS, PUSH>, dim3(grid), dim3(ts_threads(NSUB, M, KS)),
+                             (size_t)smem, st, tm, p));
     return SBVR_OK;
 }
-template <int S, int NSUB, int M>
+template <int S, int NSUB, int M, bool PUSH>
 static int ts_launch_idx(const CUtensorMap& tm, const TsParams& p, int idxb, int KS, int grid, int smem, cudaStream_t st) {
     if constexpr (NSUB == 1 && M == 1) {
         if (KS == 2) {
             switch (idxb) {
-                case 0: return ts_launch_inst<S, NSUB, M, 0, 2>(tm, p, grid, smem, st);
-                case 1: return ts_launch_inst<S, NSUB, M, 1, 2>(tm, p, grid, smem, st);
-                default: return ts_launch_inst<S, NSUB, M, 2, 2>(tm, p, grid, smem, st);
+                case 0: return ts_launch_inst<S, NSUB, M, 0, 2, PUSH>(tm, p, grid, smem, st);
+                case 1: return ts_launch_inst<S, NSUB, M, 1, 2, PUSH>(tm, p, grid, smem, st);
+                default: return ts_launch_inst<S, NSUB, M, 2, 2, PUSH>(tm, p, grid, smem, st);
             }
         }
     }
     switch (idxb) {
-        case 0: return ts_launch_inst<S, NSUB, M, 0, 1>(tm, p, grid, smem, st);
-        case 1: return ts_launch_inst<S, NSUB, M, 1, 1>(tm, p, grid, smem, st);
-        default: return ts_launch_inst<S, NSUB, M, 2, 1>(tm, p, grid, smem, st);
+        case 0: return ts_launch_inst<S, NSUB, M, 0, 1, PUSH>(tm, p, grid, smem, st);
+        case 1: return ts_launch_inst<S, NSUB, M, 1, 1, PUSH>(tm, p, grid, smem, st);
+        default: return ts_launch_inst<S, NSUB, M, 2, 1, PUSH>(tm, p, grid, smem, st);
     }
 }
-template <int S, int NSUB>
+template <int S, int NSUB, bool PUSH>
 static int ts_launch_m(const CUtensorMap& tm, const TsParams& p, int M, int idxb, int KS, int grid, int smem,
                        cudaStream_t st) {
     switch (M) {
-        case 1: return ts_launch_idx<S, NSUB, 1>(tm, p, idxb, KS, grid, smem, st);
-        case 2: return ts_launch_idx<S, NSUB, 2>(tm, p, idxb, KS, grid, smem, st);
-        case 3: return ts_launch_idx<S, NSUB, 3>(tm, p, idxb, KS, grid, smem, st);
-        default: return ts_launch_idx<S, NSUB, 4>(tm, p, idxb, KS, grid, smem, st);
+        case 1: return ts_launch_idx<S, NSUB, 1, PUSH>(tm, p, idxb, KS, grid, smem, st);
+        case 2: return ts_launch_idx<S, NSUB, 2, PUSH>(tm, p, idxb, KS, grid, smem, st);
+        case 3: return ts_launch_idx<S, NSUB, 3, PUSH>(tm, p, idxb, KS, grid, smem, st);
+        default: return ts_launch_idx<S, NSUB, 4, PUSH>(tm, p, idxb, KS, grid, smem, st);
     }
 }
+// The pushing form (tensor-parallel decode) is a kernel of its own, so that the plain one carries none of its code; it is
+// built for group length 256 only.
 template <int S>
-static int ts_launch_g(const CUtensorMap& tm, const TsParams& p, int G, int M, int idxb, int KS, int grid, int smem,
+static int ts_launch_g(const CUtensorMap& tm, const TsParams& p, bool push, int G, int M, int idxb, int KS, int grid, int smem,
                        cudaStream_t st) {
-    return G == 256 ? ts_launch_m<S, 1>(tm, p, M, idxb, KS, grid, smem, st)
-                    : ts_launch_m<S, 2>(tm, p, M, idxb, KS, grid, smem, st);
+    if (push) {
+        if (G != 256) return SBVR_ERR_UNSUPPORTED;
+        return ts_launch_m<S, 1, true>(tm, p, M, idxb, KS, grid, smem, st);
+    }
+    return G == 256 ? ts_launch_m<S, 1, false>(tm, p, M, idxb, KS, grid, smem, st)
+                    : ts_launch_m<S, 2, false>(tm, p, M, idxb, KS, grid, smem, st);
 }
 
 // `scratch` (256-byte aligned, linear_tcs_workspace_bytes long), `status` and `xchg` (SBVR_WS_XCHG_BYTES of exchange slots,
@@ -946,7 +952,7 @@ static int ts_launch_g(const CUtensorMap& tm, const TsParams& p, int G, int M, i
 // carve them differently.
 int launch_linear_tcs(const __half* x, const PackedW& w, const __half* bias, __half* y, int M, int device,
                       unsigned int* status, unsigned long long* xchg, char* scratch, size_t scratch_bytes, cudaStream_t st,
-                      const XOp* xop, const PushDst* push) {
+                      const XOp* xop, const sbvr_push_desc_t* push) {
     if (!linear_tcs_supported(w, M)) return SBVR_ERR_UNSUPPORTED;
     if (!status || !xchg || !scratch) return SBVR_ERR_WORKSPACE;
     if (reinterpret_cast<uintptr_t>(x) & 15) return SBVR_ERR_ALIGN;      // x is fetched 16 bytes at a time
@@ -1001,17 +1007,13 @@ int launch_linear_tcs(const __half* x, const PackedW& w, const __half* bias, __h
     p.pre_stages = pl.stages < 3 ? pl.stages : 3;
     p.off_red = pl.off_red, p.off_cache = pl.off_cache, p.off_ring = pl.off_ring, p.off_b = pl.off_b;
     if (push) {
-        if (!push->peer_recv || !push->step || push->world < 1 || push->rank < 0 || push->rank >= push->world || M > push->rows_max ||
-            (w.N & 1))
-            return SBVR_ERR_BAD_ARG;
-        p.push = *push;
-    } else {
-        p.push = PushDst{nullptr, nullptr, 0, 0, 0, 0, 0};
+        if (w.N & 1) return SBVR_ERR_SHAPE;
+        p.y = reinterpret_cast<__half*>(const_cast<sbvr_push_desc_t*>(push));
     }
     switch (w.S) {
-        case 2: return ts_launch_g<2>(tm, p, w.G, M, w.idx_bytes, pl.KS, pl.grid, pl.smem, st);
-        case 3: return ts_launch_g<3>(tm, p, w.G, M, w.idx_bytes, pl.KS, pl.grid, pl.smem, st);
-        default: return ts_launch_g<4>(tm, p, w.G, M, w.idx_bytes, pl.KS, pl.grid, pl.smem, st);
+        case 2: return ts_launch_g<2>(tm, p, push != nullptr, w.G, M, w.idx_bytes, pl.KS, pl.grid, pl.smem, st);
+        case 3: return ts_launch_g<3>(tm, p, push != nullptr, w.G, M, w.idx_bytes, pl.KS, pl.grid, pl.smem, st);
+        default: return ts_launch_g<4>(tm, p, push != nullptr, w.G, M, w.idx_bytes, pl.KS, pl.grid, pl.smem, st);
     }
 }
 

@@ -22,7 +22,7 @@ constexpr int PM_KQ = 4;               // K quarters per row block (one warp eac
 constexpr int PM_RB = 2;               // row blocks per CTA
 constexpr int PM_THREADS = 32 * PM_KQ * PM_RB;
 
-template <int LS, int RS>
+template <int LS, int RS, int GU>
 __global__ void __launch_bounds__(PM_THREADS) popc_mm_kernel(const uint32_t* __restrict__ l_bvr, const void* __restrict__ l_idx,
                                                              int l_idx_bytes, const __half* __restrict__ l_cache,
                                                              const uint32_t* __restrict__ r_bvr, const void* __restrict__ r_idx,
@@ -60,13 +60,14 @@ __global__ void __launch_bounds__(PM_THREADS) popc_mm_kernel(const uint32_t* __r
     float acc[PM_MT];
 #pragma unroll
     for (int m = 0; m < PM_MT; ++m) acc[m] = 0.0f;
-    // Two groups per iteration: their sixteen packed words and two coefficients are requested before the first popcount
-    // (with one group in flight per warp the weight stream was latency-bound).
-    for (int g = g0; g < g1; g += 2) {
-        uint32_t rw[2][8];
-        float cr[2];
+    // GU groups per iteration: their packed words and coefficients are requested before the first popcount.  Two groups
+    // in flight help when the grid is small (one group per warp in flight left the weight stream latency-bound:
+    // 10.2 -> 8.3 us at 4096 x 4096); with many CTAs the extra registers cost occupancy (17.7 -> 26 us at 14336 x 4096).
+    for (int g = g0; g < g1; g += GU) {
+        uint32_t rw[GU][8];
+        float cr[GU];
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
+        for (int u = 0; u < GU; ++u) {
             const bool on = live && (g + u < g1);
 #pragma unroll
             for (int kw = 0; kw < 8; ++kw) rw[u][kw] = on ? __ldcs(r_bvr + ((size_t)((g + u) * 8 + kw) * N + n) * RS + b) : 0u;
@@ -79,7 +80,7 @@ __global__ void __launch_bounds__(PM_THREADS) popc_mm_kernel(const uint32_t* __r
             }
         }
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
+        for (int u = 0; u < GU; ++u) {
             if (g + u < g1) {
 #pragma unroll
                 for (int m = 0; m < PM_MT; ++m) {
@@ -127,13 +128,26 @@ static int popc_launch(const uint32_t* l_bvr, const void* l_idx, int lib, const 
     const size_t smem = (size_t)(K / 32) * PM_MT * LS * 4 + (size_t)(K / 256) * PM_MT * LS * 4 +
                         (size_t)PM_RB * PM_KQ * PM_MT * ROWS * 4;
     if (smem > 200 * 1024) return SBVR_ERR_UNSUPPORTED;
-    static SmemOnce once;
-    const int rc_once = set_max_smem_once(once, popc_mm_kernel<LS, RS>, 200 * 1024);
+    static SmemOnce once1, once2;
+    int rc_once = set_max_smem_once(once1, popc_mm_kernel<LS, RS, 1>, 200 * 1024);
+    if (rc_once) return rc_once;
+    rc_once = set_max_smem_once(once2, popc_mm_kernel<LS, RS, 2>, 200 * 1024);
     if (rc_once) return rc_once;
     const int blocks = (N + PM_RB * ROWS - 1) / (PM_RB * ROWS);
-    for (int m0 = 0; m0 < M; m0 += PM_MT)
-        SBVR_CUDA_TRY(launch_pdl(popc_mm_kernel<LS, RS>, dim3(blocks), dim3(PM_THREADS), smem, st, l_bvr, l_idx, lib, l_cache,
-                                 r_bvr, r_idx, rib, r_cache, bias, y, M, m0, N, K));
+    int dev = 0;
+    SBVR_CUDA_TRY(cudaGetDevice(&dev));
+    DeviceInfo di;
+    const int rc_di = device_info(dev, &di);
+    if (rc_di) return rc_di;
+    const bool two = blocks <= 3 * di.sm_count;
+    for (int m0 = 0; m0 < M; m0 += PM_MT) {
+        if (two)
+            SBVR_CUDA_TRY(launch_pdl(popc_mm_kernel<LS, RS, 2>, dim3(blocks), dim3(PM_THREADS), smem, st, l_bvr, l_idx, lib, l_cache,
+                                     r_bvr, r_idx, rib, r_cache, bias, y, M, m0, N, K));
+        else
+            SBVR_CUDA_TRY(launch_pdl(popc_mm_kernel<LS, RS, 1>, dim3(blocks), dim3(PM_THREADS), smem, st, l_bvr, l_idx, lib, l_cache,
+                                     r_bvr, r_idx, rib, r_cache, bias, y, M, m0, N, K));
+    }
     return SBVR_OK;
 }
 

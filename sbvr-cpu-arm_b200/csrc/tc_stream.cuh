@@ -179,7 +179,8 @@ struct TsCursor {
 // recorded in the status words and in the CTA's abort flag; the caller then carries on as if the phase had completed
 // (its results are garbage, the host sees SBVR_ERR_TIMEOUT), and every later wait of the CTA gives up at once, so
 // that the barrier protocol of the CTA runs to its end instead of hanging.
-static __device__ __noinline__ void ts_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, unsigned int* status,
+template <int UNUSED = 0>      // a template only so that the header can be included by several translation units
+__device__ __noinline__ void ts_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, unsigned int* status,
                                           uint32_t where, bool heed_abort) {
     const long long t0 = clock64();
     for (;;) {

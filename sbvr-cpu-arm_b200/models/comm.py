@@ -43,9 +43,20 @@ class SymmetricAllReduce:
         ptrs = [int(p) for p in self.handle.buffer_ptrs]
         self.bufs_dev = torch.tensor(ptrs, dtype=torch.int64, device=device)
         self.flags_dev = torch.tensor([p + data_bytes for p in ptrs], dtype=torch.int64, device=device)
-        self.recv_dev = torch.tensor([p + recv_off for p in ptrs], dtype=torch.int64, device=device)
         self.recv_local = ptrs[self.rank] + recv_off
         self.step = torch.zeros(1, dtype=torch.int32, device=device)
+        # one push descriptor per call of a step, in device memory (sbvr_push_desc_t)
+        import ctypes
+        descs = (_lib.PushDesc * calls_per_step)()
+        for c in range(calls_per_step):
+            for r, p in enumerate(ptrs):
+                descs[c].peer_recv[r] = p + recv_off
+            descs[c].step = self.step.data_ptr()
+            descs[c].calls_per_step, descs[c].call_idx = calls_per_step, c
+            descs[c].rank, descs[c].world, descs[c].rows_max = self.rank, self.world, self.push_rows
+        raw = torch.frombuffer(bytearray(bytes(descs)), dtype=torch.uint8)
+        self.push_descs = raw.to(device)
+        self.push_desc_bytes = ctypes.sizeof(_lib.PushDesc)
         self.local = self.block[:data_bytes].view(torch.float16).view(2, max_rows, hidden)
 
     def partial_out(self, call_idx: int, rows: int) -> torch.Tensor:
@@ -74,9 +85,8 @@ class SymmetricAllReduce:
             st = torch.cuda.current_stream().cuda_stream
             ws = _lib.workspace(di, st)
             rc = _lib.lib.sbvr_linear_push_f16(x_op, x.data_ptr(), None, None, None, 0.0, b, ix, ib, c, C, _ptr(bias),
-                                               self.recv_dev.data_ptr(), self.step.data_ptr(), self.calls_per_step, call_idx,
-                                               self.rank, self.world, self.push_rows, rows, self.hidden, Kp, w.num_sums,
-                                               w.bvr_len, ws.handle, st)
+                                               self.push_descs.data_ptr() + call_idx * self.push_desc_bytes, rows,
+                                               self.hidden, Kp, w.num_sums, w.bvr_len, ws.handle, st)
         if rc == -7:
             return False
         _lib.check(rc, "sbvr_linear_push_f16")

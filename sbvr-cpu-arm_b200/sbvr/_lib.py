@@ -76,8 +76,7 @@ lib.sbvr_argmax_f16.restype = _i
 
 lib.sbvr_allreduce_add_rmsnorm_f16.argtypes = [_vp, _vp, _vp, _i, _i, _i, _i, _sz, _vp, _vp, _vp, _vp, _i, _i, _f, _vp, _vp]
 lib.sbvr_allreduce_add_rmsnorm_f16.restype = _i
-lib.sbvr_linear_push_f16.argtypes = [_i, _vp, _vp, _vp, _vp, _f, _vp, _vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i,
-                                     _i, _i, _vp, _vp]
+lib.sbvr_linear_push_f16.argtypes = [_i, _vp, _vp, _vp, _vp, _f, _vp, _vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp]
 lib.sbvr_linear_push_f16.restype = _i
 lib.sbvr_ll_reduce_add_rmsnorm_f16.argtypes = [_vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _f, _vp, _vp]
 lib.sbvr_ll_reduce_add_rmsnorm_f16.restype = _i
@@ -86,6 +85,13 @@ EXPORTS = ["sbvr_popc_mm_f16", "sbvr_linear_t_f16", "sbvr_encode_mse_f16", "sbvr
            "sbvr_embedding_f16", "sbvr_argmax_f16", "sbvr_linear_f16_noalloc", "sbvr_workspace_bytes", "sbvr_strerror", "sbvr_last_cuda_error", "sbvr_query", "sbvr_workspace_create",
            "sbvr_workspace_destroy", "sbvr_workspace_status", "sbvr_decode_f16", "sbvr_linear_f16",
            "sbvr_linear_f16_host"]
+
+
+class PushDesc(ctypes.Structure):
+    """sbvr_push_desc_t of include/sbvr_b200.h."""
+    _fields_ = [("peer_recv", ctypes.c_ulonglong * 16), ("step", ctypes.c_void_p), ("calls_per_step", ctypes.c_int),
+                ("call_idx", ctypes.c_int), ("rank", ctypes.c_int), ("world", ctypes.c_int), ("rows_max", ctypes.c_int),
+                ("reserved", ctypes.c_int)]
 
 
 def strerror(rc: int) -> str:

@@ -25,11 +25,21 @@ def _shard(N, K, S, seed, dev):
     return p, w
 
 
-def _push(L, ws, st, x_op, x, w, recv_ptrs, step, cps, call, rank, world, rows_max, M, N, K):
+def _desc(recv, step, cps, call, rank, world, rows_max, dev):
+    """An sbvr_push_desc_t in device memory whose peers are all the one local receive area."""
+    from sbvr import _lib
+    d = _lib.PushDesc()
+    for r in range(world):
+        d.peer_recv[r] = recv.data_ptr()
+    d.step = step.data_ptr()
+    d.calls_per_step, d.call_idx, d.rank, d.world, d.rows_max = cps, call, rank, world, rows_max
+    return torch.frombuffer(bytearray(bytes(d)), dtype=torch.uint8).to(dev)
+
+
+def _push(L, ws, st, x_op, x, w, desc, M, N, K):
     b, ix, ib, c, C = w._abi_args()
     return L.sbvr_linear_push_f16(x_op, x.data_ptr(), None, None, None, ctypes.c_float(0.0), b, ix, ib, c, C, None,
-                                  recv_ptrs.data_ptr(), step.data_ptr(), cps, call, rank, world, rows_max, M, N, K,
-                                  w.num_sums, w.bvr_len, ws.handle, st)
+                                  desc.data_ptr(), M, N, K, w.num_sums, w.bvr_len, ws.handle, st)
 
 
 @pytest.mark.parametrize("M", [1, 3])
@@ -43,7 +53,6 @@ def test_pushed_partials_are_reduced_like_separate_kernels(M, silu):
     st = torch.cuda.current_stream().cuda_stream
     ws = _lib.workspace(torch.cuda.current_device(), st)
     recv = torch.zeros(2 * world * rows_max * (N // 2), dtype=torch.int64, device=dev)
-    recv_ptrs = torch.tensor([recv.data_ptr()] * world, dtype=torch.int64, device=dev)
     step = torch.zeros(1, dtype=torch.int32, device=dev)
     rng = np.random.default_rng(M)
     shards = [_shard(N, Kr, 4, 40 + r, dev) for r in range(world)]
@@ -64,7 +73,8 @@ def test_pushed_partials_are_reduced_like_separate_kernels(M, silu):
                 xs.append(x)
                 parts.append(sbvr.linear(x, shards[r][1]))
         for r in range(world):
-            rc = _push(L, ws, st, 1 if silu else 0, xs[r], shards[r][1], recv_ptrs, step, cps, call, r, world, rows_max, M, N, Kr)
+            desc = _desc(recv, step, cps, call, r, world, rows_max, dev)
+            rc = _push(L, ws, st, 1 if silu else 0, xs[r], shards[r][1], desc, M, N, Kr)
             assert rc == 0, _lib.strerror(rc)
         h_out = torch.empty_like(h)
         y = torch.empty_like(h)
@@ -97,11 +107,11 @@ def test_missing_rank_runs_into_the_bounded_wait():
     ws = _lib.workspace(torch.cuda.current_device(), st)
     assert ws.status(st) == 0
     recv = torch.zeros(2 * world * rows_max * (N // 2), dtype=torch.int64, device=dev)
-    recv_ptrs = torch.tensor([recv.data_ptr()] * world, dtype=torch.int64, device=dev)
     step = torch.zeros(1, dtype=torch.int32, device=dev)
     p, w = _shard(N, Kr, 4, 9, dev)
     x = torch.randn((M, Kr), device=dev).half()
-    assert _push(L, ws, st, 0, x, w, recv_ptrs, step, cps, 0, 0, world, rows_max, M, N, Kr) == 0      # rank 1 never pushes
+    desc = _desc(recv, step, cps, 0, 0, world, rows_max, dev)
+    assert _push(L, ws, st, 0, x, w, desc, M, N, Kr) == 0      # rank 1 never pushes
     h = torch.randn((M, N), device=dev).half()
     weight = torch.ones(N, dtype=torch.float16, device=dev)
     h_out, y = torch.empty_like(h), torch.empty_like(h)
