@@ -59,11 +59,26 @@ class LlamaConfig:
             return LlamaConfig(hidden_size=512, intermediate_size=1024, num_hidden_layers=2, num_attention_heads=4,
                                num_key_value_heads=2, vocab_size=1024, codebook_lines=256,
                                max_position_embeddings=512)
-        if name == "tiny8":                        # eight KV heads: splits over up to eight tensor-parallel ranks
-            return LlamaConfig(hidden_size=1024, intermediate_size=2048, num_hidden_layers=2, num_attention_heads=8,
+        if name == "tiny8":                        # splits over up to eight tensor-parallel ranks: eight KV heads, and
+            # eight 256-column groups in the inputs of the row-parallel projections (o: hidden, down: intermediate)
+            return LlamaConfig(hidden_size=2048, intermediate_size=4096, num_hidden_layers=2, num_attention_heads=16,
                                num_key_value_heads=8, vocab_size=1024, codebook_lines=256,
                                max_position_embeddings=512)
         raise ValueError(f"unknown preset {name}")
+
+    def tp_problems(self, world: int, group_len: int = 256) -> list:
+        """Why this configuration cannot be split over `world` tensor-parallel ranks (empty list: it can)."""
+        bad = []
+        if self.num_attention_heads % world:
+            bad.append(f"{self.num_attention_heads} attention heads over {world} ranks")
+        if self.num_key_value_heads % world:
+            bad.append(f"{self.num_key_value_heads} KV heads over {world} ranks")
+        for name, k in (("hidden_size", self.hidden_size), ("intermediate_size", self.intermediate_size)):
+            if k % (world * group_len):
+                bad.append(f"{name} {k}: the row-parallel projection's input does not split into {world} x groups of {group_len}")
+        if self.vocab_size % world:
+            bad.append(f"vocabulary {self.vocab_size} over {world} ranks")
+        return bad
 
 
 def _stream() -> int:
@@ -164,6 +179,9 @@ class SBVRLlamaForCausalLM(torch.nn.Module):
         self.device = torch.device(device)
         self.tp_group = tp_group
         self.tp_size = 1 if tp_group is None else torch.distributed.get_world_size(tp_group)
+        problems = config.tp_problems(self.tp_size, config.group_len if hasattr(config, "group_len") else 256)
+        if problems:
+            raise ValueError("configuration does not split over the tensor-parallel ranks: " + "; ".join(problems))
         self.tp_rank = 0 if tp_group is None else torch.distributed.get_rank(tp_group)
         c = config
         if c.head_dim != 128:

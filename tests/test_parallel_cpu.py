@@ -87,3 +87,15 @@ def test_fuse_rows_offsets_codebooks():
     Wa = O.decode(pa["bvr"], pa["coeff_idx"], pa["coeff"], G=256)
     Wb = O.decode(pb["bvr"], pb["coeff_idx"], pb["coeff"], G=256)
     assert np.array_equal(W.view(np.uint16), np.concatenate([Wa, Wb, Wa]).view(np.uint16))
+
+
+def test_presets_split_over_the_rank_counts_they_are_used_with():
+    """The model presets the multi-GPU tests and bench.py run at 2, 4 and 8 ranks split over them: heads, KV heads,
+    vocabulary rows, and whole 256-column groups in the inputs of the row-parallel projections."""
+    sys.path.insert(0, os.path.join(ROOT, "sbvr-cpu-arm_b200"))
+    from models.sbvr_llama import LlamaConfig
+    for preset, worlds in (("tiny", (1, 2)), ("tiny8", (1, 2, 4, 8)), ("8b", (1, 2, 4, 8)), ("70b", (1, 2, 4, 8))):
+        cfg = LlamaConfig.preset(preset)
+        for world in worlds:
+            assert cfg.tp_problems(world) == [], (preset, world, cfg.tp_problems(world))
+    assert LlamaConfig.preset("tiny").tp_problems(8)          # 512 hidden columns are not eight groups of 256
