@@ -272,10 +272,14 @@ SBVR_API int sbvr_linear_push_f16(int x_op, const void* x, const void* delta, co
                                   const uint32_t* bvr, const void* coeff_idx, int idx_bytes, const void* coeff, int C,
                                   const void* bias, const sbvr_push_desc_t* push_desc_dev, int M, int N, int K, int S, int G,
                                   sbvr_workspace_t* ws, sbvr_stream_t stream);
+/* follows_push = 1 promises that the kernel launched on `stream` directly before this call is the sbvr_linear_push_f16
+ * of the same call_idx, and that h_in, weight and the step counter were final before that linear: the kernel then does
+ * not wait for the linear to end (the linear lets it start only after its own inputs were complete; the packets announce
+ * themselves).  With 0 it waits for everything in front of it on the stream like any other kernel of the library. */
 SBVR_API int sbvr_ll_reduce_add_rmsnorm_f16(const void* recv_local, const int* step_dev, int calls_per_step, int call_idx,
                                             int world, int rows_max, const void* h_in, const void* weight, void* h_out,
-                                            void* y, int rows, int hidden, float eps, sbvr_workspace_t* ws,
-                                            sbvr_stream_t stream);
+                                            void* y, int rows, int hidden, float eps, int follows_push,
+                                            sbvr_workspace_t* ws, sbvr_stream_t stream);
 
 #ifdef __cplusplus
 }

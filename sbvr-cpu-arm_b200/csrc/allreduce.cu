@@ -150,10 +150,14 @@ __device__ __forceinline__ ulonglong2 ld_volatile_v2(const unsigned long long* p
 __global__ void __launch_bounds__(1024) ll_reduce_add_rmsnorm_kernel(
     const unsigned long long* __restrict__ recv,      // [2][world][rows_max][hidden / 2]
     const int* __restrict__ step_ptr, int calls_per_step, int call_idx, int world, int rows_max, const __half* h_in,
-    const __half* __restrict__ weight, __half* h_out, __half* __restrict__ y, int hidden, float eps, unsigned int* status) {
+    const __half* __restrict__ weight, __half* h_out, __half* __restrict__ y, int hidden, float eps, unsigned int* status,
+    int follows_push) {
     __shared__ float red[32];
     pdl_launch_dependents();
-    pdl_wait();                                    // the residual and the step counter belong to earlier kernels until now
+    // Directly behind the pushing GEMV of the same call this kernel is only let go once that GEMV's own dependency wait
+    // has returned: the residual and the step counter are final, the packets announce themselves, and nothing else of
+    // the GEMV is read, so its end (and the acknowledgement of its stores to the peers) need not be waited for.
+    if (!follows_push) pdl_wait();
     const unsigned int epoch = (unsigned int)(*step_ptr) * (unsigned int)calls_per_step + (unsigned int)call_idx + 1u;
     const size_t row = (size_t)blockIdx.x * hidden;
     const int nvec = hidden / 8;
@@ -261,8 +265,8 @@ extern "C" int sbvr_allreduce_add_rmsnorm_f16(const void* peer_bufs_dev, const v
 
 extern "C" int sbvr_ll_reduce_add_rmsnorm_f16(const void* recv_local, const int* step_dev, int calls_per_step, int call_idx,
                                                int world, int rows_max, const void* h_in, const void* weight, void* h_out,
-                                               void* y, int rows, int hidden, float eps, sbvr_workspace_t* ws,
-                                               sbvr_stream_t stream) {
+                                               void* y, int rows, int hidden, float eps, int follows_push,
+                                               sbvr_workspace_t* ws, sbvr_stream_t stream) {
     if (!recv_local || !step_dev || !h_in || !weight || !h_out || !y || !ws) return SBVR_ERR_BAD_ARG;
     if (world < 1 || world > AR_MAX_WORLD || rows < 1 || rows > rows_max || calls_per_step < 1 || call_idx < 0 ||
         call_idx >= calls_per_step || (calls_per_step & 1))
@@ -271,10 +275,10 @@ extern "C" int sbvr_ll_reduce_add_rmsnorm_f16(const void* recv_local, const int*
     if ((reinterpret_cast<uintptr_t>(recv_local) | reinterpret_cast<uintptr_t>(h_in) | reinterpret_cast<uintptr_t>(weight) |
          reinterpret_cast<uintptr_t>(h_out) | reinterpret_cast<uintptr_t>(y)) & 15)
         return SBVR_ERR_ALIGN;
-    SBVR_CUDA_TRY(launch_pdl(ll_reduce_add_rmsnorm_kernel, dim3(rows), dim3(hidden >= 8192 ? 1024 : 512), 0,
+    SBVR_CUDA_TRY(launch_pdl(ll_reduce_add_rmsnorm_kernel, dim3(rows), dim3(512), 0,
                              reinterpret_cast<cudaStream_t>(stream), reinterpret_cast<const unsigned long long*>(recv_local),
                              step_dev, calls_per_step, call_idx, world, rows_max, reinterpret_cast<const __half*>(h_in),
                              reinterpret_cast<const __half*>(weight), reinterpret_cast<__half*>(h_out),
-                             reinterpret_cast<__half*>(y), hidden, eps, ws->status));
+                             reinterpret_cast<__half*>(y), hidden, eps, ws->status, follows_push ? 1 : 0));
     return SBVR_OK;
 }

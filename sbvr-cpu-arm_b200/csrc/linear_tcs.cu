@@ -180,7 +180,10 @@ template <int S, int NSUB, int M, int IDXB, int KS, bool PUSH>
 __global__ void __launch_bounds__(ts_threads(NSUB, M, KS), 1)
     linear_tcs_kernel(const __grid_constant__ CUtensorMap tmap, const TsParams p) {
     static_assert(KS == 1 || (KS == 2 && NSUB == 1 && M == 1), "two blocks per step: one activation row, one group per block");
-    pdl_launch_dependents();                       // the next kernel on the stream may be scheduled as SMs free up
+    // The next kernel on the stream may be scheduled as SMs free up.  The pushing form lets it go later, from the finisher
+    // warp once this kernel's own dependency wait has returned: its consumer (sbvr_ll_reduce_add_rmsnorm_f16) then knows
+    // that everything in front of this kernel is complete and does not wait for this kernel to end.
+    if (!PUSH) pdl_launch_dependents();
     extern __shared__ __align__(1024) unsigned char smem[];
     constexpr int SP = ts_sp(S);
     constexpr int TN = ts_tn(S);
@@ -304,6 +307,7 @@ __global__ void __launch_bounds__(ts_threads(NSUB, M, KS), 1)
         __syncwarp();
         if (lane == 0) mbar_arrive(tmem_ready);    // whoever needs tensor memory waits for this
         pdl_wait();                                // digits, scratch and y belong to the stream's earlier kernels until now
+        if (PUSH) pdl_launch_dependents();
         digits_share([] {});
         if (lane == 0 && !p.x_in_kernel) {
             const uint32_t dig = (uint32_t)(KB * M * 1024);
@@ -422,7 +426,7 @@ __global__ void __launch_bounds__(ts_threads(NSUB, M, KS), 1)
             }
             if (PUSH && fin) {
                 // Tensor parallel: (two fp16 outputs | epoch << 32) to slot [epoch parity][this rank] of every rank's receive
-                // area, one 8-byte store per peer and pair (M * TN is a multiple of 32: a warp's 32 values are valid together).
+                // area (M * TN is a multiple of 32: a warp's 32 values are valid together).
                 const sbvr_push_desc_t* pd = reinterpret_cast<const sbvr_push_desc_t*>(p.y);
                 const int world = pd->world;
                 const unsigned int epoch = (unsigned int)(*pd->step) * (unsigned int)pd->calls_per_step + (unsigned int)pd->call_idx + 1u;
@@ -433,15 +437,19 @@ __global__ void __launch_bounds__(ts_threads(NSUB, M, KS), 1)
                     if (i < M * TN) {
                         const int m = i / TN, nl = i % TN;
                         const float b = p.bias ? __half2float(p.bias[n0 + nl]) : 0.0f;
+                        // four neighbouring outputs meet in one lane: two packets, one 16-byte store per peer
                         const unsigned int h = __half_as_ushort(__float2half_rn(v[e] + b));
-                        const unsigned int hn = __shfl_down_sync(0xffffffffu, h, 1);
-                        if ((lane & 1) == 0) {
-                            const unsigned long long pk = (unsigned long long)(h | (hn << 16)) | ((unsigned long long)epoch << 32);
+                        const unsigned int h1 = __shfl_down_sync(0xffffffffu, h, 1);
+                        const unsigned int h2 = __shfl_down_sync(0xffffffffu, h, 2);
+                        const unsigned int h3 = __shfl_down_sync(0xffffffffu, h, 3);
+                        if ((lane & 3) == 0) {
+                            const unsigned long long pk0 = (unsigned long long)(h | (h1 << 16)) | ((unsigned long long)epoch << 32);
+                            const unsigned long long pk1 = (unsigned long long)(h2 | (h3 << 16)) | ((unsigned long long)epoch << 32);
                             const size_t at = (slot + m) * (size_t)(N / 2) + (size_t)((n0 + nl) >> 1);
                             for (int r = 0; r < world; ++r)
-                                asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(
+                                asm volatile("st.volatile.global.v2.u64 [%0], {%1, %2};" ::"l"(
                                                  reinterpret_cast<unsigned long long*>(pd->peer_recv[r]) + at),
-                                             "l"(pk)
+                                             "l"(pk0), "l"(pk1)
                                              : "memory");
                         }
                     }
@@ -1007,7 +1015,7 @@ int launch_linear_tcs(const __half* x, const PackedW& w, const __half* bias, __h
     p.pre_stages = pl.stages < 3 ? pl.stages : 3;
     p.off_red = pl.off_red, p.off_cache = pl.off_cache, p.off_ring = pl.off_ring, p.off_b = pl.off_b;
     if (push) {
-        if (w.N & 1) return SBVR_ERR_SHAPE;
+        if (w.N & 3) return SBVR_ERR_SHAPE;
         p.y = reinterpret_cast<__half*>(const_cast<sbvr_push_desc_t*>(push));
     }
     switch (w.S) {

@@ -94,9 +94,11 @@ class SymmetricAllReduce:
 
     def ll_reduce_add_rmsnorm(self, call_idx: int, h: torch.Tensor, weight: torch.Tensor, y: torch.Tensor, rows: int,
                               eps: float, ws, stream: int):
+        """Must be the launch directly behind push_linear(call_idx, ...) on the stream: it does not wait for that linear
+        to end (h and the norm weight are final long before it)."""
         _lib.check(_lib.lib.sbvr_ll_reduce_add_rmsnorm_f16(
             self.recv_local, self.step.data_ptr(), self.calls_per_step, call_idx, self.world, self.push_rows,
-            h.data_ptr(), weight.data_ptr(), h.data_ptr(), y.data_ptr(), rows, self.hidden, eps, ws.handle, stream),
+            h.data_ptr(), weight.data_ptr(), h.data_ptr(), y.data_ptr(), rows, self.hidden, eps, 1, ws.handle, stream),
             "sbvr_ll_reduce_add_rmsnorm_f16")
 
     def end_step(self):

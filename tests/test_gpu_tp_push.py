@@ -80,7 +80,7 @@ def test_pushed_partials_are_reduced_like_separate_kernels(M, silu):
         y = torch.empty_like(h)
         rc = L.sbvr_ll_reduce_add_rmsnorm_f16(recv.data_ptr(), step.data_ptr(), cps, call, world, rows_max, h.data_ptr(),
                                               weight.data_ptr(), h_out.data_ptr(), y.data_ptr(), M, N, ctypes.c_float(1e-5),
-                                              ws.handle, st)
+                                              1 if it % 2 == 0 else 0, ws.handle, st)
         assert rc == 0, _lib.strerror(rc)
         assert ws.status(st) == 0
         # the same arithmetic with the separate kernels' results: fp32 sum of the fp16 partials in rank order, one rounding
@@ -118,7 +118,7 @@ def test_missing_rank_runs_into_the_bounded_wait():
     t0 = time.perf_counter()
     rc = L.sbvr_ll_reduce_add_rmsnorm_f16(recv.data_ptr(), step.data_ptr(), cps, 0, world, rows_max, h.data_ptr(),
                                           weight.data_ptr(), h_out.data_ptr(), y.data_ptr(), M, N, ctypes.c_float(1e-5),
-                                          ws.handle, st)
+                                          1, ws.handle, st)
     assert rc == 0
     status = ws.status(st)
     assert status == -6, _lib.strerror(status)            # SBVR_ERR_TIMEOUT
