@@ -20,11 +20,36 @@
 // call e) only after call e + 1, which needs every peer's flag of e + 1, which a peer raises only after its call e
 // has finished reading.  The epoch is step * calls_per_step + call + 1 with `step` read from device memory, so a
 // captured CUDA graph can be replayed: the host bumps `step` once per decode step inside the graph.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
 namespace sbvr {
 
 constexpr int AR_MAX_WORLD = 16;
+constexpr int AR_CLUSTER = 8;                           // CTAs that share a row (thread-block cluster, sums meet in shared memory)
+
+// A row is split by columns over the CTAs of a cluster (one SM moved a row of 8192 at about 64 B per clock: 2-3 us of a
+// 9 us all-reduce); the sum of squares of the row is the sum of the CTAs' parts, read from each other's shared memory.
+__device__ __forceinline__ float cluster_row_sum(float part, float* red /* [33] shared */) {
+    namespace cg = cooperative_groups;
+#pragma unroll
+    for (int o = 16; o; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = part;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.0f;
+        for (int w = 0; w < (int)((blockDim.x + 31) >> 5); ++w) t += red[w];
+        red[32] = t;
+    }
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();                                     // every CTA's part is in its shared memory
+    float tot = 0.0f;
+    for (unsigned int r = 0; r < cluster.num_blocks(); ++r) tot += *cluster.map_shared_rank(&red[32], r);
+    cluster.sync();                                     // nobody leaves while its part may still be read
+    return tot;
+}
+
 constexpr unsigned int AR_POLL_LIMIT = 1u << 22;        // polls of about 50 ns each
 
 __device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
@@ -42,12 +67,14 @@ __global__ void __launch_bounds__(1024) allreduce_add_rmsnorm_kernel(
     const int* __restrict__ step_ptr, int calls_per_step, int call_idx, int rank, int world, size_t buf_elems,
     const __half* h_in, const __half* __restrict__ weight, __half* h_out, __half* __restrict__ y, int hidden, float eps,
     unsigned int* status) {
-    __shared__ float red[32];
+    __shared__ float red[33];
     __shared__ int ok_s;
     pdl_launch_dependents();
     pdl_wait();                                    // the partial of this rank (previous kernel) is complete from here on
     const unsigned int epoch = (unsigned int)(*step_ptr) * (unsigned int)calls_per_step + (unsigned int)call_idx + 1u;
     const size_t parity_off = (size_t)(call_idx & 1) * buf_elems;
+    const int nslice = (int)cooperative_groups::this_cluster().num_blocks();
+    const int row_idx = blockIdx.x / nslice, slice = blockIdx.x % nslice;
     if (blockIdx.x == 0 && threadIdx.x < world) {
         __threadfence_system();
         st_release_sys(reinterpret_cast<unsigned int*>(peer_flags[threadIdx.x]) + rank, epoch);
@@ -69,12 +96,14 @@ __global__ void __launch_bounds__(1024) allreduce_add_rmsnorm_kernel(
         }
     }
     __syncthreads();
-    if (!ok_s) return;
+    // a CTA whose wait ran out carries on with what it has (the host sees the time-out): the cluster barriers below
+    // need every CTA
 
-    const size_t row = (size_t)blockIdx.x * hidden;
+    const size_t row = (size_t)row_idx * hidden;
     const int nvec = hidden / 8;
+    const int v0 = slice * (nvec / nslice), v1 = v0 + nvec / nslice;
     float ss = 0.0f;
-    for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+    for (int i = v0 + threadIdx.x; i < v1; i += blockDim.x) {
         float acc[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) acc[e] = 0.0f;
@@ -110,14 +139,9 @@ __global__ void __launch_bounds__(1024) allreduce_add_rmsnorm_kernel(
         }
         *reinterpret_cast<uint4*>(h_out + row + (size_t)i * 8) = a;
     }
-#pragma unroll
-    for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
-    __syncthreads();
-    float tot = 0.0f;
-    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) tot += red[w];
+    const float tot = cluster_row_sum(ss, red);
     const float rs = rsqrtf(tot / (float)hidden + eps);
-    for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+    for (int i = v0 + threadIdx.x; i < v1; i += blockDim.x) {
         const uint4 a = *reinterpret_cast<const uint4*>(h_out + row + (size_t)i * 8);     // written above by this thread
         const uint4 wv = *reinterpret_cast<const uint4*>(weight + (size_t)i * 8);
         const __half2* ah = reinterpret_cast<const __half2*>(&a);
@@ -152,17 +176,20 @@ __global__ void __launch_bounds__(1024) ll_reduce_add_rmsnorm_kernel(
     const int* __restrict__ step_ptr, int calls_per_step, int call_idx, int world, int rows_max, const __half* h_in,
     const __half* __restrict__ weight, __half* h_out, __half* __restrict__ y, int hidden, float eps, unsigned int* status,
     int follows_push) {
-    __shared__ float red[32];
+    __shared__ float red[33];
     pdl_launch_dependents();
     // Directly behind the pushing GEMV of the same call this kernel is only let go once that GEMV's own dependency wait
     // has returned: the residual and the step counter are final, the packets announce themselves, and nothing else of
     // the GEMV is read, so its end (and the acknowledgement of its stores to the peers) need not be waited for.
     if (!follows_push) pdl_wait();
     const unsigned int epoch = (unsigned int)(*step_ptr) * (unsigned int)calls_per_step + (unsigned int)call_idx + 1u;
-    const size_t row = (size_t)blockIdx.x * hidden;
+    const int nslice = (int)cooperative_groups::this_cluster().num_blocks();
+    const int row_idx = blockIdx.x / nslice, slice = blockIdx.x % nslice;
+    const size_t row = (size_t)row_idx * hidden;
     const int nvec = hidden / 8;
+    const int v0 = slice * (nvec / nslice), v1 = v0 + nvec / nslice;
     float ss = 0.0f;
-    for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+    for (int i = v0 + threadIdx.x; i < v1; i += blockDim.x) {
         float acc[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) acc[e] = 0.0f;
@@ -175,7 +202,7 @@ __global__ void __launch_bounds__(1024) ll_reduce_add_rmsnorm_kernel(
                 for (int u = 0; u < 8; ++u) {
                     const int r = (r0 + u < world) ? r0 + u : r0;
                     const unsigned long long* src =
-                        recv + (((size_t)(call_idx & 1) * world + r) * rows_max + blockIdx.x) * (size_t)(hidden / 2) + (size_t)i * 4;
+                        recv + (((size_t)(call_idx & 1) * world + r) * rows_max + row_idx) * (size_t)(hidden / 2) + (size_t)i * 4;
                     a[u] = ld_volatile_v2(src);
                     b[u] = ld_volatile_v2(src + 2);
                 }
@@ -214,14 +241,9 @@ __global__ void __launch_bounds__(1024) ll_reduce_add_rmsnorm_kernel(
         }
         *reinterpret_cast<uint4*>(h_out + row + (size_t)i * 8) = hv;
     }
-#pragma unroll
-    for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
-    __syncthreads();
-    float tot = 0.0f;
-    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) tot += red[w];
+    const float tot = cluster_row_sum(ss, red);
     const float rs = rsqrtf(tot / (float)hidden + eps);
-    for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+    for (int i = v0 + threadIdx.x; i < v1; i += blockDim.x) {
         const uint4 hv = *reinterpret_cast<const uint4*>(h_out + row + (size_t)i * 8);    // written above by this thread
         const uint4 wv = *reinterpret_cast<const uint4*>(weight + (size_t)i * 8);
         const __half2* ah = reinterpret_cast<const __half2*>(&hv);
@@ -254,7 +276,10 @@ extern "C" int sbvr_allreduce_add_rmsnorm_f16(const void* peer_bufs_dev, const v
     if ((reinterpret_cast<uintptr_t>(h_in) | reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(h_out) |
          reinterpret_cast<uintptr_t>(y)) & 15)
         return SBVR_ERR_ALIGN;
-    SBVR_CUDA_TRY(launch_pdl(allreduce_add_rmsnorm_kernel, dim3(rows), dim3(hidden >= 8192 ? 1024 : 512), 0, reinterpret_cast<cudaStream_t>(stream),
+    // a row is shared by a cluster of CTAs where its 16-byte chunks divide evenly
+    const int nvec = hidden / 8, cs = (nvec % AR_CLUSTER == 0) ? AR_CLUSTER : 1;
+    const int per = nvec / cs, threads = per >= 512 ? 512 : (per + 31) / 32 * 32;
+    SBVR_CUDA_TRY(launch_pdl_cluster(allreduce_add_rmsnorm_kernel, dim3(rows * cs), dim3(threads), cs, 0, reinterpret_cast<cudaStream_t>(stream),
                              reinterpret_cast<const unsigned long long*>(peer_bufs_dev),
                              reinterpret_cast<const unsigned long long*>(peer_flags_dev), step_dev, calls_per_step, call_idx,
                              rank, world, buf_elems, reinterpret_cast<const __half*>(h_in),
@@ -275,7 +300,9 @@ extern "C" int sbvr_ll_reduce_add_rmsnorm_f16(const void* recv_local, const int*
     if ((reinterpret_cast<uintptr_t>(recv_local) | reinterpret_cast<uintptr_t>(h_in) | reinterpret_cast<uintptr_t>(weight) |
          reinterpret_cast<uintptr_t>(h_out) | reinterpret_cast<uintptr_t>(y)) & 15)
         return SBVR_ERR_ALIGN;
-    SBVR_CUDA_TRY(launch_pdl(ll_reduce_add_rmsnorm_kernel, dim3(rows), dim3(512), 0,
+    const int nvec = hidden / 8, cs = (nvec % AR_CLUSTER == 0) ? AR_CLUSTER : 1;
+    const int per = nvec / cs, threads = per >= 512 ? 512 : (per + 31) / 32 * 32;
+    SBVR_CUDA_TRY(launch_pdl_cluster(ll_reduce_add_rmsnorm_kernel, dim3(rows * cs), dim3(threads), cs, 0,
                              reinterpret_cast<cudaStream_t>(stream), reinterpret_cast<const unsigned long long*>(recv_local),
                              step_dev, calls_per_step, call_idx, world, rows_max, reinterpret_cast<const __half*>(h_in),
                              reinterpret_cast<const __half*>(weight), reinterpret_cast<__half*>(h_out),
