@@ -760,7 +760,8 @@ def kernel_case(which):
         w = sbvr.sbvr(W, encoder_config={"num_sums": S}, device=dev, verbose_level=0)
         print(json.dumps({"kernel_case": which, **w.encoder_stats}))
         return
-    M = {"gemv": 1, "gemm16": 16, "gemm2048": 2048}[which]
+    M = {"gemv": 1, "gemm16": 16, "batch16": 16, "gemm2048": 2048}[which]
+    algo = 3 if which == "gemm16" else 0                  # M = 16: the fp16 GEMM on request, else the automatic choice
     ws_ = []
     for _ in range(6):
         bvr = torch.randint(-2**31, 2**31 - 1, (K // 32, N, S), dtype=torch.int32, device=dev, generator=gen)
@@ -771,7 +772,7 @@ def kernel_case(which):
     y = torch.empty((M, N), dtype=torch.float16, device=dev)
     for _ in range(3):
         for w in ws_:
-            sbvr.linear(x, w, None, out=y)
+            sbvr.linear(x, w, None, algo=algo, out=y)
     torch.cuda.synchronize()
     print(json.dumps({"kernel_case": which, "launches": 18, "mean_abs_y": float(y.float().abs().mean())}))
 
@@ -785,7 +786,7 @@ def main():
     ap.add_argument("--no-extras", action="store_true",
                     help="only the headline GEMV measurement (no M sweep, prefill GEMM or Llama decode sections)")
     ap.add_argument("--skip-70b", action="store_true", help="leave the 70B decode out of the Llama section")
-    ap.add_argument("--kernel-case", default=None, choices=["gemv", "gemm16", "gemm2048", "decode_step", "rowdeq", "encode"],
+    ap.add_argument("--kernel-case", default=None, choices=["gemv", "gemm16", "batch16", "gemm2048", "decode_step", "rowdeq", "encode"],
                     help="run a few launches of one kernel on 14336x4096 weights, or one eager decode step of a "
                          "4-layer Llama-3-8B-shaped model inside the NVTX range 'decode', and exit (for profilers)")
     args = ap.parse_args()
