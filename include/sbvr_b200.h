@@ -124,7 +124,8 @@ SBVR_API int sbvr_linear_f16_host(const void* x_host, const uint32_t* bvr, const
  *     current.
  *   - M <= 4 runs on the decode kernel (about 4 K M bytes of activation digits + 150 KB of partial sums: always
  *     fits); larger M runs on the batched tensor-core kernel, whose re-tiled activations (about 2 M K bytes) and
- *     split-K partial sums must fit the array: M = 128 at K = 14336 fits, M = 2048 does not.  A problem that does not
+ *     split-K partial sums must fit the array (about 2.9 MB of it): M = 16 at K = 4096 and M = 64 at K = 14336 fit,
+ *     M = 2048 does not.  A problem that does not
  *     fit returns SBVR_ERR_NOALLOC_LIMIT and launches nothing.  Shapes neither kernel covers run on the SIMT kernel,
  *     which needs no scratch.
  * It has no counterpart in the reference, whose bindings allocate their output on every call
