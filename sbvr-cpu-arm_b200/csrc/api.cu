@@ -205,7 +205,7 @@ int sbvr_linear_f16(const void* x, const uint32_t* bvr, const void* coeff_idx, i
             if (linear_tcs_supported(w, M) && !(reinterpret_cast<uintptr_t>(x) & 15) &&
                 linear_tcs_workspace_bytes(w, M, di.sm_count) <= ws->dyn_bytes) algo = 2;
             // up to 16 rows on weights large enough to give every SM eight (tile group, k block) steps: measured faster
-            // than the fp16 GEMM there (28.7 against 34.4 us at 14336 x 4096, M = 16), slower on small weights
+            // than the fp16 GEMM there (26.3 against 34.3 us at 14336 x 4096, M = 16), slower on small weights
             else if (M <= 16 && linear_tcb_supported(w, M) &&
                      (size_t)(w.N / (w.S == 2 ? 64 : 32) / 3) * (size_t)(w.K / 256) >= (size_t)8 * di.sm_count &&
                      linear_tcb_workspace_bytes(w, M, di.sm_count) <= ws->dyn_bytes) algo = 4;

@@ -28,7 +28,7 @@
 // them complete.  Every wait is bounded.
 //
 // Measured (B200, rotating weights larger than L2, CUDA graph, quantiser kernel included): 14336 x 4096, S = 4:
-// 26 us at M = 2, 28.7 us at M = 16, 36 us at M = 32 (the fp16 GEMM with in-kernel dequantisation: 34-35 us); a step of
+// 24 us at M = 2, 26.3 us at M = 16, 34.6 us at M = 32 (the fp16 GEMM with in-kernel dequantisation: 34-35 us); a step of
 // three tiles takes about 1 500 cycles, bound by the latency chain of a compute warp (barrier, tensor-memory load,
 // expansion, store drain), not by the tensor pipe (12 or 24 MMAs of 17 cycles) nor by memory.
 //
