@@ -226,9 +226,13 @@ SBVR_API int sbvr_argmax_f16(const void* logits, int* out, float* scratch, int r
  *                         (pitch K), delta NULL = no add; h + delta is also stored to h_out (may be NULL; must be a
  *                         buffer other than h and delta: both are still being read while it is written; overlap is
  *                         refused with SBVR_ERR_BAD_ARG) (LlamaDecoderLayer.forward :395-406 + LlamaRMSNorm.forward :118-123)
+ *   SBVR_XOP_DIGITS       x (still required: the rows as fp16, for the checks) has ALREADY been quantised into this
+ *                         workspace by the kernel launched directly before on this stream: one of the two all-reduce +
+ *                         RMSNorm calls below with emit_digits = 1 for the same M and K.  Saves the quantiser launch of
+ *                         rows longer than 4096.  Group length 256 only.
  * Same rounding as sbvr_silu_mul_f16 / sbvr_add_rmsnorm_f16 followed by sbvr_linear_f16.  Returns
  * SBVR_ERR_UNSUPPORTED where the decode GEMV does not apply (the caller then runs the separate kernels). */
-enum { SBVR_XOP_NONE = 0, SBVR_XOP_SILU_MUL = 1, SBVR_XOP_ADD_RMSNORM = 2 };
+enum { SBVR_XOP_NONE = 0, SBVR_XOP_SILU_MUL = 1, SBVR_XOP_ADD_RMSNORM = 2, SBVR_XOP_DIGITS = 3 };
 SBVR_API int sbvr_linear_fused_f16(int x_op, const void* x, const void* delta, const void* norm_weight, void* h_out,
                                    float eps, const uint32_t* bvr, const void* coeff_idx, int idx_bytes, const void* coeff,
                                    int C, const void* bias, void* y, int M, int N, int K, int S, int G,
@@ -248,6 +252,14 @@ SBVR_API int sbvr_allreduce_add_rmsnorm_f16(const void* peer_bufs_dev, const voi
                                             int calls_per_step, int call_idx, int rank, int world, size_t buf_elems,
                                             const void* h_in, const void* weight, void* h_out, void* y, int rows,
                                             int hidden, float eps, sbvr_workspace_t* ws, sbvr_stream_t stream);
+/* The same call that also leaves y as activation digits of the decode GEMV in the workspace (emit_digits = 1; rows <= 4,
+ * hidden a multiple of 2048, group length 256), for an sbvr_linear_fused_f16(SBVR_XOP_DIGITS, ...) with K = hidden launched
+ * directly behind it on the same stream and workspace.  SBVR_ERR_UNSUPPORTED (nothing launched) where that form does not apply. */
+SBVR_API int sbvr_allreduce_add_rmsnorm_digits_f16(const void* peer_bufs_dev, const void* peer_flags_dev, const int* step_dev,
+                                                   int calls_per_step, int call_idx, int rank, int world, size_t buf_elems,
+                                                   const void* h_in, const void* weight, void* h_out, void* y, int rows,
+                                                   int hidden, float eps, int emit_digits, sbvr_workspace_t* ws,
+                                                   sbvr_stream_t stream);
 
 /* ---- tensor parallel, decode: the all-reduce folded into the row-parallel GEMV and its consumer ----------------
  * sbvr_linear_push_f16 is sbvr_linear_fused_f16 (x_op may also be SBVR_XOP_NONE) whose result does not go to y: the
@@ -281,6 +293,11 @@ SBVR_API int sbvr_ll_reduce_add_rmsnorm_f16(const void* recv_local, const int* s
                                             int world, int rows_max, const void* h_in, const void* weight, void* h_out,
                                             void* y, int rows, int hidden, float eps, int follows_push,
                                             sbvr_workspace_t* ws, sbvr_stream_t stream);
+SBVR_API int sbvr_ll_reduce_add_rmsnorm_digits_f16(const void* recv_local, const int* step_dev, int calls_per_step,
+                                                   int call_idx, int world, int rows_max, const void* h_in,
+                                                   const void* weight, void* h_out, void* y, int rows, int hidden, float eps,
+                                                   int follows_push, int emit_digits, sbvr_workspace_t* ws,
+                                                   sbvr_stream_t stream);
 
 #ifdef __cplusplus
 }

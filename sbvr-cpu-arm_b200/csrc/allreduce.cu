@@ -23,6 +23,7 @@
 #include <cooperative_groups.h>
 
 #include "common.cuh"
+#include "xdigits.cuh"
 
 namespace sbvr {
 
@@ -61,14 +62,33 @@ __device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) 
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
+
+// The normalised row as activation digits of the decode GEMV (layout of xquant_kernel in linear_tcs.cu: [k block][row][1024 B]
+// then one fp32 step per (row, k block)), written next to y: a warp's 32 chunks of 8 values are one 256-k block.  `area` is
+// this warp's 1 KB of shared memory.
+__device__ __forceinline__ void ar_emit_digits(unsigned char* area, const uint4& o, int chunk, int row, int rows, int KB,
+                                               unsigned char* xq) {
+    const int lane = threadIdx.x & 31;
+    const int kb = chunk >> 5;
+    reinterpret_cast<uint4*>(area)[lane] = o;
+    __syncwarp();
+    float* steps = reinterpret_cast<float*>(xq + (size_t)KB * rows * 1024) + ((size_t)row * KB + kb);
+    xdigits_block<1>(area, steps, lane);
+    __syncwarp();
+    uint4* dst = reinterpret_cast<uint4*>(xq + ((size_t)kb * rows + row) * 1024);
+    dst[lane] = reinterpret_cast<const uint4*>(area)[lane];
+    dst[lane + 32] = reinterpret_cast<const uint4*>(area)[lane + 32];
+}
+
 __global__ void __launch_bounds__(1024) allreduce_add_rmsnorm_kernel(
     const unsigned long long* __restrict__ peer_bufs,    // [world] base address of every rank's buffer area
     const unsigned long long* __restrict__ peer_flags,   // [world] base address of every rank's flag array
     const int* __restrict__ step_ptr, int calls_per_step, int call_idx, int rank, int world, size_t buf_elems,
     const __half* h_in, const __half* __restrict__ weight, __half* h_out, __half* __restrict__ y, int hidden, float eps,
-    unsigned int* status) {
+    unsigned int* status, unsigned char* xq) {
     __shared__ float red[33];
     __shared__ int ok_s;
+    __shared__ __align__(16) unsigned char dig_area[16][1024];
     pdl_launch_dependents();
     pdl_wait();                                    // the partial of this rank (previous kernel) is complete from here on
     const unsigned int epoch = (unsigned int)(*step_ptr) * (unsigned int)calls_per_step + (unsigned int)call_idx + 1u;
@@ -154,6 +174,7 @@ __global__ void __launch_bounds__(1024) allreduce_add_rmsnorm_kernel(
             oh[e] = __hmul2(wh[e], __floats2half2_rn(f.x * rs, f.y * rs));
         }
         *reinterpret_cast<uint4*>(y + row + (size_t)i * 8) = o;
+        if (xq) ar_emit_digits(dig_area[threadIdx.x >> 5], o, i, row_idx, (int)(gridDim.x / nslice), hidden / 256, xq);
     }
 }
 
@@ -175,8 +196,9 @@ __global__ void __launch_bounds__(1024) ll_reduce_add_rmsnorm_kernel(
     const unsigned long long* __restrict__ recv,      // [2][world][rows_max][hidden / 2]
     const int* __restrict__ step_ptr, int calls_per_step, int call_idx, int world, int rows_max, const __half* h_in,
     const __half* __restrict__ weight, __half* h_out, __half* __restrict__ y, int hidden, float eps, unsigned int* status,
-    int follows_push) {
+    int follows_push, unsigned char* xq) {
     __shared__ float red[33];
+    __shared__ __align__(16) unsigned char dig_area[16][1024];
     pdl_launch_dependents();
     // Directly behind the pushing GEMV of the same call this kernel is only let go once that GEMV's own dependency wait
     // has returned: the residual and the step counter are final, the packets announce themselves, and nothing else of
@@ -256,6 +278,7 @@ __global__ void __launch_bounds__(1024) ll_reduce_add_rmsnorm_kernel(
             oh[e] = __hmul2(wh[e], __floats2half2_rn(f.x * rs, f.y * rs));
         }
         *reinterpret_cast<uint4*>(y + row + (size_t)i * 8) = o;
+        if (xq) ar_emit_digits(dig_area[threadIdx.x >> 5], o, i, row_idx, (int)(gridDim.x / nslice), hidden / 256, xq);
     }
 }
 
@@ -263,10 +286,23 @@ __global__ void __launch_bounds__(1024) ll_reduce_add_rmsnorm_kernel(
 
 using namespace sbvr;
 
-extern "C" int sbvr_allreduce_add_rmsnorm_f16(const void* peer_bufs_dev, const void* peer_flags_dev, const int* step_dev,
-                                               int calls_per_step, int call_idx, int rank, int world, size_t buf_elems,
-                                               const void* h_in, const void* weight, void* h_out, void* y, int rows,
-                                               int hidden, float eps, sbvr_workspace_t* ws, sbvr_stream_t stream) {
+// Where the digits go: the start of the workspace's dynamic region, which is where the decode GEMV looks for them.
+static int ar_digits_target(sbvr_workspace_t* ws, int rows, int hidden, int emit_digits, unsigned char** xq) {
+    *xq = nullptr;
+    if (!emit_digits) return SBVR_OK;
+    const int nvec = hidden / 8;
+    if (rows > 4 || hidden % 2048 || nvec % AR_CLUSTER || (nvec / AR_CLUSTER) % 32 || nvec / AR_CLUSTER > 512) return SBVR_ERR_UNSUPPORTED;
+    const size_t need = (size_t)(hidden / 256) * rows * 1024 + (((size_t)rows * (hidden / 256) * 4 + 15) / 16) * 16;
+    if (need > ws->dyn_bytes) return SBVR_ERR_WORKSPACE;
+    *xq = reinterpret_cast<unsigned char*>(ws->dyn);
+    return SBVR_OK;
+}
+
+extern "C" int sbvr_allreduce_add_rmsnorm_digits_f16(const void* peer_bufs_dev, const void* peer_flags_dev, const int* step_dev,
+                                                      int calls_per_step, int call_idx, int rank, int world, size_t buf_elems,
+                                                      const void* h_in, const void* weight, void* h_out, void* y, int rows,
+                                                      int hidden, float eps, int emit_digits, sbvr_workspace_t* ws,
+                                                      sbvr_stream_t stream) {
     if (!peer_bufs_dev || !peer_flags_dev || !step_dev || !h_in || !weight || !h_out || !y || !ws) return SBVR_ERR_BAD_ARG;
     if (world < 1 || world > AR_MAX_WORLD || rank < 0 || rank >= world || rows < 1 || calls_per_step < 1 || call_idx < 0 ||
         call_idx >= calls_per_step || (calls_per_step & 1))
@@ -276,6 +312,9 @@ extern "C" int sbvr_allreduce_add_rmsnorm_f16(const void* peer_bufs_dev, const v
     if ((reinterpret_cast<uintptr_t>(h_in) | reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(h_out) |
          reinterpret_cast<uintptr_t>(y)) & 15)
         return SBVR_ERR_ALIGN;
+    unsigned char* xq = nullptr;
+    const int rc = ar_digits_target(ws, rows, hidden, emit_digits, &xq);
+    if (rc) return rc;
     // a row is shared by a cluster of CTAs where its 16-byte chunks divide evenly
     const int nvec = hidden / 8, cs = (nvec % AR_CLUSTER == 0) ? AR_CLUSTER : 1;
     const int per = nvec / cs, threads = per >= 512 ? 512 : (per + 31) / 32 * 32;
@@ -284,14 +323,23 @@ extern "C" int sbvr_allreduce_add_rmsnorm_f16(const void* peer_bufs_dev, const v
                              reinterpret_cast<const unsigned long long*>(peer_flags_dev), step_dev, calls_per_step, call_idx,
                              rank, world, buf_elems, reinterpret_cast<const __half*>(h_in),
                              reinterpret_cast<const __half*>(weight), reinterpret_cast<__half*>(h_out),
-                             reinterpret_cast<__half*>(y), hidden, eps, ws->status));
+                             reinterpret_cast<__half*>(y), hidden, eps, ws->status, xq));
     return SBVR_OK;
 }
 
-extern "C" int sbvr_ll_reduce_add_rmsnorm_f16(const void* recv_local, const int* step_dev, int calls_per_step, int call_idx,
-                                               int world, int rows_max, const void* h_in, const void* weight, void* h_out,
-                                               void* y, int rows, int hidden, float eps, int follows_push,
-                                               sbvr_workspace_t* ws, sbvr_stream_t stream) {
+extern "C" int sbvr_allreduce_add_rmsnorm_f16(const void* peer_bufs_dev, const void* peer_flags_dev, const int* step_dev,
+                                               int calls_per_step, int call_idx, int rank, int world, size_t buf_elems,
+                                               const void* h_in, const void* weight, void* h_out, void* y, int rows,
+                                               int hidden, float eps, sbvr_workspace_t* ws, sbvr_stream_t stream) {
+    return sbvr_allreduce_add_rmsnorm_digits_f16(peer_bufs_dev, peer_flags_dev, step_dev, calls_per_step, call_idx, rank, world,
+                                                 buf_elems, h_in, weight, h_out, y, rows, hidden, eps, 0, ws, stream);
+}
+
+extern "C" int sbvr_ll_reduce_add_rmsnorm_digits_f16(const void* recv_local, const int* step_dev, int calls_per_step,
+                                                      int call_idx, int world, int rows_max, const void* h_in,
+                                                      const void* weight, void* h_out, void* y, int rows, int hidden, float eps,
+                                                      int follows_push, int emit_digits, sbvr_workspace_t* ws,
+                                                      sbvr_stream_t stream) {
     if (!recv_local || !step_dev || !h_in || !weight || !h_out || !y || !ws) return SBVR_ERR_BAD_ARG;
     if (world < 1 || world > AR_MAX_WORLD || rows < 1 || rows > rows_max || calls_per_step < 1 || call_idx < 0 ||
         call_idx >= calls_per_step || (calls_per_step & 1))
@@ -300,12 +348,23 @@ extern "C" int sbvr_ll_reduce_add_rmsnorm_f16(const void* recv_local, const int*
     if ((reinterpret_cast<uintptr_t>(recv_local) | reinterpret_cast<uintptr_t>(h_in) | reinterpret_cast<uintptr_t>(weight) |
          reinterpret_cast<uintptr_t>(h_out) | reinterpret_cast<uintptr_t>(y)) & 15)
         return SBVR_ERR_ALIGN;
+    unsigned char* xq = nullptr;
+    const int rc = ar_digits_target(ws, rows, hidden, emit_digits, &xq);
+    if (rc) return rc;
     const int nvec = hidden / 8, cs = (nvec % AR_CLUSTER == 0) ? AR_CLUSTER : 1;
     const int per = nvec / cs, threads = per >= 512 ? 512 : (per + 31) / 32 * 32;
     SBVR_CUDA_TRY(launch_pdl_cluster(ll_reduce_add_rmsnorm_kernel, dim3(rows * cs), dim3(threads), cs, 0,
                              reinterpret_cast<cudaStream_t>(stream), reinterpret_cast<const unsigned long long*>(recv_local),
                              step_dev, calls_per_step, call_idx, world, rows_max, reinterpret_cast<const __half*>(h_in),
                              reinterpret_cast<const __half*>(weight), reinterpret_cast<__half*>(h_out),
-                             reinterpret_cast<__half*>(y), hidden, eps, ws->status, follows_push ? 1 : 0));
+                             reinterpret_cast<__half*>(y), hidden, eps, ws->status, follows_push ? 1 : 0, xq));
     return SBVR_OK;
+}
+
+extern "C" int sbvr_ll_reduce_add_rmsnorm_f16(const void* recv_local, const int* step_dev, int calls_per_step, int call_idx,
+                                               int world, int rows_max, const void* h_in, const void* weight, void* h_out,
+                                               void* y, int rows, int hidden, float eps, int follows_push,
+                                               sbvr_workspace_t* ws, sbvr_stream_t stream) {
+    return sbvr_ll_reduce_add_rmsnorm_digits_f16(recv_local, step_dev, calls_per_step, call_idx, world, rows_max, h_in, weight,
+                                                 h_out, y, rows, hidden, eps, follows_push, 0, ws, stream);
 }

@@ -233,7 +233,7 @@ int sbvr_linear_fused_f16(int x_op, const void* x, const void* delta, const void
     int rc = make_packed(&w, bvr, coeff_idx, idx_bytes, coeff, C, N, K, S, G);
     if (rc) return rc;
     if (!x || !y || M < 1) return SBVR_ERR_BAD_ARG;
-    if (x_op != SBVR_XOP_SILU_MUL && x_op != SBVR_XOP_ADD_RMSNORM) return SBVR_ERR_BAD_ARG;
+    if (x_op != SBVR_XOP_SILU_MUL && x_op != SBVR_XOP_ADD_RMSNORM && x_op != SBVR_XOP_DIGITS) return SBVR_ERR_BAD_ARG;
     if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(y) & 1)) return SBVR_ERR_ALIGN;
     DeviceInfo di;
     if (!ws) return SBVR_ERR_WORKSPACE;

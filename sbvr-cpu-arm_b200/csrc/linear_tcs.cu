@@ -1001,7 +1001,9 @@ int launch_linear_tcs(const __half* x, const PackedW& w, const __half* bias, __h
     // get the separate kernel
     const int NWG = ts_nwg(256 / w.G, M, pl.KS);
     const bool in_kernel = (xp.x_op == SBVR_XOP_NONE) && (M * pl.KB <= ts_cw0(256 / w.G, M, pl.KS) + 4 * NWG);
-    if (!in_kernel) {
+    // SBVR_XOP_DIGITS: the digits are in the scratch already (written by the reduce kernel in front of this call)
+    if (xp.x_op == SBVR_XOP_DIGITS && w.G != 256) return SBVR_ERR_UNSUPPORTED;
+    if (!in_kernel && xp.x_op != SBVR_XOP_DIGITS) {
         const dim3 qgrid((pl.KB + 15) / 16, M);
         if (w.G == 256) SBVR_CUDA_TRY(launch_pdl(xquant_kernel<1>, qgrid, dim3(512), 0, st, xp));
         else SBVR_CUDA_TRY(launch_pdl(xquant_kernel<2>, qgrid, dim3(512), 0, st, xp));

@@ -63,12 +63,29 @@ class SymmetricAllReduce:
         """Where the row-parallel linear of call `call_idx` of this step writes its [rows, hidden] partial."""
         return self.local[call_idx & 1, :rows]
 
+    def emits_digits(self, rows: int) -> bool:
+        """Whether the reduce kernels can leave their result as activation digits for a decode GEMV that would otherwise
+        launch a quantiser kernel of its own (rows longer than 4096 elements, up to four of them)."""
+        return rows <= 4 and self.hidden % 2048 == 0 and rows * (self.hidden // 256) > 16
+
     def reduce_add_rmsnorm(self, call_idx: int, h: torch.Tensor, weight: torch.Tensor, y: torch.Tensor, rows: int,
-                           eps: float, ws, stream: int):
+                           eps: float, ws, stream: int, emit_digits: bool = False) -> bool:
+        """Returns whether the digits were written (emit_digits asked for and supported)."""
+        rc = -7
+        if emit_digits:
+            rc = _lib.lib.sbvr_allreduce_add_rmsnorm_digits_f16(
+                self.bufs_dev.data_ptr(), self.flags_dev.data_ptr(), self.step.data_ptr(), self.calls_per_step, call_idx,
+                self.rank, self.world, self.buf_elems, h.data_ptr(), weight.data_ptr(), h.data_ptr(), y.data_ptr(), rows,
+                self.hidden, eps, 1, ws.handle, stream)
+            if rc == 0:
+                return True
+            if rc not in (-7, -5):
+                _lib.check(rc, "sbvr_allreduce_add_rmsnorm_digits_f16")
         _lib.check(_lib.lib.sbvr_allreduce_add_rmsnorm_f16(
             self.bufs_dev.data_ptr(), self.flags_dev.data_ptr(), self.step.data_ptr(), self.calls_per_step, call_idx,
             self.rank, self.world, self.buf_elems, h.data_ptr(), weight.data_ptr(), h.data_ptr(), y.data_ptr(), rows,
             self.hidden, eps, ws.handle, stream), "sbvr_allreduce_add_rmsnorm_f16")
+        return False
 
     def push_linear(self, call_idx: int, x_op: int, x: torch.Tensor, w, rows: int, bias=None) -> bool:
         """The row-parallel linear of call `call_idx`, its result pushed to every rank's receive area.  False (nothing
@@ -93,13 +110,22 @@ class SymmetricAllReduce:
         return True
 
     def ll_reduce_add_rmsnorm(self, call_idx: int, h: torch.Tensor, weight: torch.Tensor, y: torch.Tensor, rows: int,
-                              eps: float, ws, stream: int):
+                              eps: float, ws, stream: int, emit_digits: bool = False) -> bool:
         """Must be the launch directly behind push_linear(call_idx, ...) on the stream: it does not wait for that linear
-        to end (h and the norm weight are final long before it)."""
+        to end (h and the norm weight are final long before it).  Returns whether the digits were written."""
+        if emit_digits:
+            rc = _lib.lib.sbvr_ll_reduce_add_rmsnorm_digits_f16(
+                self.recv_local, self.step.data_ptr(), self.calls_per_step, call_idx, self.world, self.push_rows,
+                h.data_ptr(), weight.data_ptr(), h.data_ptr(), y.data_ptr(), rows, self.hidden, eps, 1, 1, ws.handle, stream)
+            if rc == 0:
+                return True
+            if rc not in (-7, -5):
+                _lib.check(rc, "sbvr_ll_reduce_add_rmsnorm_digits_f16")
         _lib.check(_lib.lib.sbvr_ll_reduce_add_rmsnorm_f16(
             self.recv_local, self.step.data_ptr(), self.calls_per_step, call_idx, self.world, self.push_rows,
             h.data_ptr(), weight.data_ptr(), h.data_ptr(), y.data_ptr(), rows, self.hidden, eps, 1, ws.handle, stream),
             "sbvr_ll_reduce_add_rmsnorm_f16")
+        return False
 
     def end_step(self):
         self.step.add_(1)

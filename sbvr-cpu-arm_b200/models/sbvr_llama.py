@@ -24,7 +24,7 @@ import torch
 
 import sbvr as _sbvr
 from sbvr import _lib
-from sbvr.core import XOP_ADD_RMSNORM, XOP_NONE, XOP_SILU_MUL, linear_fused
+from sbvr.core import XOP_ADD_RMSNORM, XOP_DIGITS, XOP_NONE, XOP_SILU_MUL, linear_fused
 from sbvr.core import linear as sbvr_linear
 from sbvr.core import sbvr as sbvr_tensor
 
@@ -354,10 +354,12 @@ class SBVRLlamaForCausalLM(torch.nn.Module):
             lin(b.xn, out=out)
 
         ck(L.sbvr_embedding_f16(b.ids.data_ptr(), self.embed_tokens.data_ptr(), hc.data_ptr(), T, H, st), "embedding")
-        delta, normed = None, False
+        delta, normed, digits = None, False, False
         for li, layer in enumerate(self.layers):
             if normed:
-                layer.qkv_proj(b.xn, out=b.qkv)
+                if not (digits and linear_fused(XOP_DIGITS, b.xn, layer.qkv_proj.weight, b.qkv, bias=layer.qkv_proj.bias)):
+                    layer.qkv_proj(b.xn, out=b.qkv)
+                digits = False
             else:
                 norm_linear(layer.qkv_proj, delta, layer.input_layernorm_weight, b.qkv)
             att_scratch = None if b.att_scratch is None else b.att_scratch.data_ptr()
@@ -376,13 +378,19 @@ class SBVRLlamaForCausalLM(torch.nn.Module):
                                         self.n_heads, self.n_kv, c.head_dim, self.max_ctx, scale, nsplit, st), "attention")
             if comm is not None:
                 # decode: the o projection pushes its result into every rank's receive area (no separate all-reduce)
+                # rows longer than 4096: the reduce kernel also leaves the normalised rows as the digits of the next GEMV
+                want = fuse and comm.emits_digits(T) and isinstance(layer.gate_up_proj, SBVRLinear)
                 if fuse and self.pushed_allreduce and isinstance(layer.o_proj, SBVRLinear) and comm.push_linear(
                         2 * li, XOP_NONE, b.ao, layer.o_proj.weight, T, bias=layer.o_proj.bias):
-                    comm.ll_reduce_add_rmsnorm(2 * li, hc, layer.post_attention_layernorm_weight, b.xn, T, eps, ws, st)
+                    have = comm.ll_reduce_add_rmsnorm(2 * li, hc, layer.post_attention_layernorm_weight, b.xn, T, eps, ws,
+                                                      st, emit_digits=want)
                 else:
                     layer.o_proj(b.ao, out=comm.partial_out(2 * li, T))
-                    comm.reduce_add_rmsnorm(2 * li, hc, layer.post_attention_layernorm_weight, b.xn, T, eps, ws, st)
-                layer.gate_up_proj(b.xn, out=b.gu)
+                    have = comm.reduce_add_rmsnorm(2 * li, hc, layer.post_attention_layernorm_weight, b.xn, T, eps, ws, st,
+                                                   emit_digits=want)
+                if not (have and linear_fused(XOP_DIGITS, b.xn, layer.gate_up_proj.weight, b.gu,
+                                              bias=layer.gate_up_proj.bias)):
+                    layer.gate_up_proj(b.xn, out=b.gu)
             else:
                 layer.o_proj(b.ao, out=b.o)
                 self._all_reduce(b.o)
@@ -396,10 +404,12 @@ class SBVRLlamaForCausalLM(torch.nn.Module):
                 layer.down_proj(b.act, out=down_out)
             if comm is not None:
                 nw = self.layers[li + 1].input_layernorm_weight if li + 1 < n_layers else self.norm_weight
+                nxt = self.layers[li + 1].qkv_proj if li + 1 < n_layers else None      # (lm_head rows may be selected first)
+                want = fuse and comm.emits_digits(T) and isinstance(nxt, SBVRLinear)
                 if pushed:
-                    comm.ll_reduce_add_rmsnorm(2 * li + 1, hc, nw, b.xn, T, eps, ws, st)
+                    digits = comm.ll_reduce_add_rmsnorm(2 * li + 1, hc, nw, b.xn, T, eps, ws, st, emit_digits=want)
                 else:
-                    comm.reduce_add_rmsnorm(2 * li + 1, hc, nw, b.xn, T, eps, ws, st)
+                    digits = comm.reduce_add_rmsnorm(2 * li + 1, hc, nw, b.xn, T, eps, ws, st, emit_digits=want)
                 delta, normed = None, True
             else:
                 self._all_reduce(b.down)

@@ -326,7 +326,7 @@ def linear(x: torch.Tensor, w: sbvr, bias: Optional[torch.Tensor] = None, algo: 
     return y.view(*lead, N)
 
 
-XOP_NONE, XOP_SILU_MUL, XOP_ADD_RMSNORM = 0, 1, 2
+XOP_NONE, XOP_SILU_MUL, XOP_ADD_RMSNORM, XOP_DIGITS = 0, 1, 2, 3
 
 
 @torch.inference_mode()
@@ -335,7 +335,9 @@ def linear_fused(op: int, x: torch.Tensor, w: sbvr, out: torch.Tensor, delta: Op
                  bias: Optional[torch.Tensor] = None) -> bool:
     """Decode linear with the op in front of it folded into the kernel (`sbvr_linear_fused_f16`):
     XOP_SILU_MUL: out = (silu(x[:, :K]) * x[:, K:]) @ W.T;  XOP_ADD_RMSNORM: out = rmsnorm(x + delta) * norm_weight @ W.T
-    with x + delta stored to h_out.  Returns False (and computes nothing) where the decode kernel does not apply."""
+    with x + delta stored to h_out;  XOP_DIGITS: out = x @ W.T where the kernel launched directly before on this stream
+    (an all-reduce + RMSNorm with emit_digits) has already left x quantised in the stream's workspace.
+    Returns False (and computes nothing) where the decode kernel does not apply."""
     dev = w.bvr.device
     di = _cuda_index(dev)
     Kp, N = w.in_features_padded, w.out_features

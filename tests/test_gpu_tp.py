@@ -26,9 +26,11 @@ def _worker(rank, world, port, q):
         dev = torch.device("cuda", rank)
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev,
                                 timeout=datetime.timedelta(seconds=90))
-        cfg = LlamaConfig.preset("tiny" if world <= 2 else "tiny8")
-        tp = SBVRLlamaForCausalLM(cfg, device=dev, tp_group=dist.group.WORLD, max_batch=2, max_ctx=64).init_synthetic(3)
-        ids = torch.randint(0, cfg.vocab_size, (2, 24), device=dev, generator=torch.Generator(device=dev).manual_seed(9))
+        # tiny8 splits over 1 .. 8 ranks; three sequences: decode steps of three rows go through the pushed all-reduce and
+        # (hidden 2048: 3 x 8 k blocks) through the reduce kernels' digit output for the following GEMV
+        cfg = LlamaConfig.preset("tiny8")
+        tp = SBVRLlamaForCausalLM(cfg, device=dev, tp_group=dist.group.WORLD, max_batch=3, max_ctx=64).init_synthetic(3)
+        ids = torch.randint(0, cfg.vocab_size, (3, 24), device=dev, generator=torch.Generator(device=dev).manual_seed(9))
         logits = tp(ids).float()
         a = tp.generate(ids, 10, use_graph=False)
         b = tp.generate(ids, 10, use_graph=True)
@@ -46,7 +48,7 @@ def _worker(rank, world, port, q):
             raise RuntimeError("symmetric memory set-up failed: " + getattr(tp, "_comm_error", "?"))
         err = -1.0
         if rank == 0:
-            one = SBVRLlamaForCausalLM(cfg, device=dev, max_batch=2, max_ctx=64).init_synthetic(3)
+            one = SBVRLlamaForCausalLM(cfg, device=dev, max_batch=3, max_ctx=64).init_synthetic(3)
             ref = one(ids).float()
             err = ((logits - ref).abs().max() / ref.abs().max()).item()
         q.put((rank, "ok", err, same))

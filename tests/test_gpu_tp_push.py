@@ -129,3 +129,51 @@ def test_missing_rank_runs_into_the_bounded_wait():
     yy = sbvr.linear(x, w).cpu().numpy()
     ref = O.linear_c(x.cpu().numpy(), p["bvr"], p["coeff_idx"], p["coeff"], G=256)
     assert O.max_rel_err(yy, ref) <= 1e-2
+
+
+@pytest.mark.parametrize("M", [1, 2])
+@pytest.mark.parametrize("pushed", [True, False])
+def test_reduce_kernels_leave_the_digits_of_the_next_gemv(M, pushed):
+    """emit_digits: the all-reduce + RMSNorm kernel also writes its result as the activation digits of the decode GEMV into
+    the workspace, and the following sbvr_linear_fused_f16(SBVR_XOP_DIGITS) gives the bits of the ordinary linear on y."""
+    import sbvr
+    from sbvr import _lib
+    from sbvr.core import XOP_DIGITS, linear_fused
+    L = _lib.lib
+    dev = torch.device("cuda")
+    H, Kr, N2, world, rows_max, cps = 2048, 1024, 768, 2, 4, 2
+    st = torch.cuda.current_stream().cuda_stream
+    ws = _lib.workspace(torch.cuda.current_device(), st)
+    rng = np.random.default_rng(10 + M)
+    shards = [_shard(H, Kr, 4, 60 + r, dev) for r in range(world)]
+    _, w2 = _shard(N2, H, 4, 70, dev)
+    h = torch.from_numpy(rng.standard_normal((M, H)).astype(np.float16)).to(dev)
+    weight = torch.from_numpy((1.0 + 0.1 * rng.standard_normal(H)).astype(np.float16)).to(dev)
+    xs = [torch.from_numpy(rng.standard_normal((M, Kr)).astype(np.float16)).to(dev) for _ in range(world)]
+    step = torch.zeros(1, dtype=torch.int32, device=dev)
+    h_out, y = torch.empty_like(h), torch.empty_like(h)
+    if pushed:
+        recv = torch.zeros(2 * world * rows_max * (H // 2), dtype=torch.int64, device=dev)
+        for r in range(world):
+            assert _push(L, ws, st, 0, xs[r], shards[r][1], _desc(recv, step, cps, 0, r, world, rows_max, dev), M, H, Kr) == 0
+        rc = L.sbvr_ll_reduce_add_rmsnorm_digits_f16(recv.data_ptr(), step.data_ptr(), cps, 0, world, rows_max, h.data_ptr(),
+                                                     weight.data_ptr(), h_out.data_ptr(), y.data_ptr(), M, H,
+                                                     ctypes.c_float(1e-5), 1, 1, ws.handle, st)
+    else:
+        # one-shot form with a world of one: this rank's partial is the sum of the two shards' results
+        part = (sbvr.linear(xs[0], shards[0][1]).float() + sbvr.linear(xs[1], shards[1][1]).float()).half()
+        buf = torch.zeros(2 * M * H, dtype=torch.float16, device=dev)
+        buf[:M * H] = part.reshape(-1)
+        flags = torch.zeros(4, dtype=torch.int32, device=dev)
+        bufs = torch.tensor([buf.data_ptr()], dtype=torch.int64, device=dev)
+        fl = torch.tensor([flags.data_ptr()], dtype=torch.int64, device=dev)
+        rc = L.sbvr_allreduce_add_rmsnorm_digits_f16(bufs.data_ptr(), fl.data_ptr(), step.data_ptr(), cps, 0, 0, 1,
+                                                     ctypes.c_size_t(M * H), h.data_ptr(), weight.data_ptr(), h_out.data_ptr(),
+                                                     y.data_ptr(), M, H, ctypes.c_float(1e-5), 1, ws.handle, st)
+    assert rc == 0, _lib.strerror(rc)
+    out = torch.empty((M, N2), dtype=torch.float16, device=dev)
+    assert linear_fused(XOP_DIGITS, y, w2, out)
+    torch.cuda.synchronize()
+    assert ws.status(st) == 0
+    ref = sbvr.linear(y, w2)
+    assert torch.equal(out, ref)
