@@ -88,7 +88,9 @@ __global__ void __launch_bounds__(1024) allreduce_add_rmsnorm_kernel(
     unsigned int* status, unsigned char* xq) {
     __shared__ float red[33];
     __shared__ int ok_s;
-    __shared__ __align__(16) unsigned char dig_area[16][1024];
+    // 1 KB per warp, present only in launches that emit digits (a fixed 16 KB would keep this kernel from becoming resident
+    // beside the pushing GEMV, whose CTA leaves about 11 KB of an SM's shared memory free)
+    extern __shared__ __align__(16) unsigned char dig_area[];
     pdl_launch_dependents();
     pdl_wait();                                    // the partial of this rank (previous kernel) is complete from here on
     const unsigned int epoch = (unsigned int)(*step_ptr) * (unsigned int)calls_per_step + (unsigned int)call_idx + 1u;
@@ -174,7 +176,7 @@ __global__ void __launch_bounds__(1024) allreduce_add_rmsnorm_kernel(
             oh[e] = __hmul2(wh[e], __floats2half2_rn(f.x * rs, f.y * rs));
         }
         *reinterpret_cast<uint4*>(y + row + (size_t)i * 8) = o;
-        if (xq) ar_emit_digits(dig_area[threadIdx.x >> 5], o, i, row_idx, (int)(gridDim.x / nslice), hidden / 256, xq);
+        if (xq) ar_emit_digits(dig_area + (threadIdx.x >> 5) * 1024, o, i, row_idx, (int)(gridDim.x / nslice), hidden / 256, xq);
     }
 }
 
@@ -198,7 +200,9 @@ __global__ void __launch_bounds__(1024) ll_reduce_add_rmsnorm_kernel(
     const __half* __restrict__ weight, __half* h_out, __half* __restrict__ y, int hidden, float eps, unsigned int* status,
     int follows_push, unsigned char* xq) {
     __shared__ float red[33];
-    __shared__ __align__(16) unsigned char dig_area[16][1024];
+    // 1 KB per warp, present only in launches that emit digits (a fixed 16 KB would keep this kernel from becoming resident
+    // beside the pushing GEMV, whose CTA leaves about 11 KB of an SM's shared memory free)
+    extern __shared__ __align__(16) unsigned char dig_area[];
     pdl_launch_dependents();
     // Directly behind the pushing GEMV of the same call this kernel is only let go once that GEMV's own dependency wait
     // has returned: the residual and the step counter are final, the packets announce themselves, and nothing else of
@@ -278,7 +282,7 @@ __global__ void __launch_bounds__(1024) ll_reduce_add_rmsnorm_kernel(
             oh[e] = __hmul2(wh[e], __floats2half2_rn(f.x * rs, f.y * rs));
         }
         *reinterpret_cast<uint4*>(y + row + (size_t)i * 8) = o;
-        if (xq) ar_emit_digits(dig_area[threadIdx.x >> 5], o, i, row_idx, (int)(gridDim.x / nslice), hidden / 256, xq);
+        if (xq) ar_emit_digits(dig_area + (threadIdx.x >> 5) * 1024, o, i, row_idx, (int)(gridDim.x / nslice), hidden / 256, xq);
     }
 }
 
@@ -318,7 +322,7 @@ extern "C" int sbvr_allreduce_add_rmsnorm_digits_f16(const void* peer_bufs_dev, 
     // a row is shared by a cluster of CTAs where its 16-byte chunks divide evenly
     const int nvec = hidden / 8, cs = (nvec % AR_CLUSTER == 0) ? AR_CLUSTER : 1;
     const int per = nvec / cs, threads = per >= 512 ? 512 : (per + 31) / 32 * 32;
-    SBVR_CUDA_TRY(launch_pdl_cluster(allreduce_add_rmsnorm_kernel, dim3(rows * cs), dim3(threads), cs, 0, reinterpret_cast<cudaStream_t>(stream),
+    SBVR_CUDA_TRY(launch_pdl_cluster(allreduce_add_rmsnorm_kernel, dim3(rows * cs), dim3(threads), cs, xq ? (size_t)(threads / 32) * 1024 : 0, reinterpret_cast<cudaStream_t>(stream),
                              reinterpret_cast<const unsigned long long*>(peer_bufs_dev),
                              reinterpret_cast<const unsigned long long*>(peer_flags_dev), step_dev, calls_per_step, call_idx,
                              rank, world, buf_elems, reinterpret_cast<const __half*>(h_in),
@@ -353,7 +357,7 @@ extern "C" int sbvr_ll_reduce_add_rmsnorm_digits_f16(const void* recv_local, con
     if (rc) return rc;
     const int nvec = hidden / 8, cs = (nvec % AR_CLUSTER == 0) ? AR_CLUSTER : 1;
     const int per = nvec / cs, threads = per >= 512 ? 512 : (per + 31) / 32 * 32;
-    SBVR_CUDA_TRY(launch_pdl_cluster(ll_reduce_add_rmsnorm_kernel, dim3(rows * cs), dim3(threads), cs, 0,
+    SBVR_CUDA_TRY(launch_pdl_cluster(ll_reduce_add_rmsnorm_kernel, dim3(rows * cs), dim3(threads), cs, xq ? (size_t)(threads / 32) * 1024 : 0,
                              reinterpret_cast<cudaStream_t>(stream), reinterpret_cast<const unsigned long long*>(recv_local),
                              step_dev, calls_per_step, call_idx, world, rows_max, reinterpret_cast<const __half*>(h_in),
                              reinterpret_cast<const __half*>(weight), reinterpret_cast<__half*>(h_out),
