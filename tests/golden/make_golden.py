@@ -66,7 +66,9 @@ def product(ref_w, x, bias):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("SBVR_REFERENCE_DIR", "")
+    if not ref_root:
+        sys.exit("usage: make_golden.py <path of a checkout of the reference>  (or SBVR_REFERENCE_DIR)")
     core = load_reference(ref_root)
     cpu = torch.device("cpu")
     out = {}
