@@ -666,6 +666,14 @@ __global__ void __launch_bounds__(ts_threads(NSUB, M, KS), 1)
             cc.start(sg, w);
             deposit_until(cc.done(sg) ? sg.nseg : cc.q);      // segments before this warpgroup's first step
         }
+        // The warpgroups would all start their first step in the same cycle: warpgroup w starts 200 w cycles late.  Measured
+        // (graph over rotating weights, M = 1): 5.97 -> 5.72 us at 4096 x 4096, 5.27 -> 5.01 at 1024 x 4096, 11.91 -> 11.47 at
+        // 4096 x 14336, 10.71 -> 10.66 at 14336 x 4096; 100 and 300 cycles gain about half of that, 800 cycles lose 3 %.
+        if (w > 0 && n_w > 1) {
+            const long long t0 = clock64();
+            while (clock64() - t0 < (long long)w * 200) {
+            }
+        }
         float s1[NGRP][M], s2[NGRP][M];            // scales of steps i-1, i-2
         int dep1 = -1, dep2 = -1;                  // deposit up to this segment after step i-1 / i-2 (-1: nothing)
 #pragma unroll
