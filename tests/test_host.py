@@ -140,3 +140,22 @@ def test_encoder_config_and_search_space_on_cpu():
     assert bool((a[:, 1:] >= a[:, :-1]).all())
     with pytest.raises(RuntimeError):
         encoder.encode(d.view(1, -1), encoder.EncoderConfig(), device=torch.device("cpu"))
+
+
+def test_step_partition_of_the_streaming_kernels(tmp_path):
+    """The split of (tile, k step) work over the CTAs that the decode GEMV and the small-batch kernel share (TsSegs in
+    csrc/tc_stream.cuh) is compiled for the host and checked over a few thousand (tiles, steps, CTAs) combinations: every
+    step owned once, shared segments first and at most two per CTA, owners of the left-over steps as cta_of() says."""
+    import shutil
+    import subprocess
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(nvcc):
+        pytest.skip("nvcc not available")
+    exe = str(tmp_path / "partition_check")
+    src = os.path.join(ROOT, "tests", "native", "partition_check.cu")
+    subprocess.check_call([nvcc, "-std=c++17", "-O1", "-gencode", "arch=compute_100a,code=sm_100a",
+                           "-I", os.path.join(ROOT, "include"), "-I", os.path.join(ROOT, "sbvr-cpu-arm_b200", "csrc"),
+                           "-o", exe, src])
+    out = subprocess.run([exe], capture_output=True, text=True)
+    assert out.returncode == 0, out.stdout[-2000:]
+    assert "0 failures" in out.stdout
