@@ -263,10 +263,20 @@ def run_ours(args):
     if not args.no_extras:
         if world == 1:
             extra.update(small_m_and_prefill(torch, dev, stream))
-        decodes = [llama_decode(torch, dev, dist, world, "8b", 1, 512, 256)]
+        def decode_section(*a):
+            # one rank: a failing section is reported, the line is still printed (with several ranks an exception on one
+            # of them must end the job: the others wait in collectives)
+            if dist:
+                return llama_decode(torch, dev, dist, world, *a)
+            try:
+                return llama_decode(torch, dev, dist, world, *a)
+            except Exception as e:
+                torch.cuda.empty_cache()
+                return {"model": a[0], "batch": a[1], "error": str(e)[:200]}
+        decodes = [decode_section("8b", 1, 512, 256)]
         if not args.skip_70b:
-            decodes.append(llama_decode(torch, dev, dist, world, "70b", 1, 1024, 256))
-            decodes.append(llama_decode(torch, dev, dist, world, "70b", 16, 1024, 64))
+            decodes.append(decode_section("70b", 1, 1024, 256))
+            decodes.append(decode_section("70b", 16, 1024, 64))
         extra["llama_decode"] = decodes
     for (d, s_), w in _lib._workspaces.items():
         assert w.status(s_) == 0, "a device-side wait timed out during the benchmark"
@@ -564,7 +574,15 @@ def small_m_and_prefill(torch, dev, stream):
     rel = float(((we.decode().float() - Wd.float()) ** 2).mean() / (Wd.float() ** 2).mean())
     enc = {"shape": [4096, 4096], "S": S, "seconds": round(dt, 3), "groups_per_s": round(65536 / dt),
            "relative_mse": round(rel, 5), **we.encoder_stats}
-    return {"small_m_sweep": {"G": G, "index": "u16 codebook C=4096", "rows": sweep},
+    # a bounded wait that ran out in any of the launches above is reported here (and cleared), not in a later section
+    from sbvr import _lib
+    timeouts = []
+    torch.cuda.synchronize()
+    for (d_, st_), ws_obj in list(_lib._workspaces.items()):
+        if ws_obj.status(st_) != 0:
+            timeouts.append(hex(_lib.lib.sbvr_last_timeout_where()))
+    return {"bounded_wait_timeouts": timeouts,
+            "small_m_sweep": {"G": G, "index": "u16 codebook C=4096", "rows": sweep},
             "group128_direct": {"rows": direct128},
             "small_batch_kernels": {"rows": batch},
             "other_formulations_m1": others, "prefill_gemm": prefill,
@@ -761,7 +779,7 @@ def kernel_case(which):
         print(json.dumps({"kernel_case": which, **w.encoder_stats}))
         return
     M = {"gemv": 1, "gemm16": 16, "batch16": 16, "gemm2048": 2048}[which]
-    algo = 3 if which == "gemm16" else 0                  # M = 16: the fp16 GEMM on request, else the automatic choice
+    algo = {"gemm16": 3, "batch16": 4}.get(which, 0)      # M = 16: the fp16 GEMM or the small-batch FP4 kernel on request
     ws_ = []
     for _ in range(6):
         bvr = torch.randint(-2**31, 2**31 - 1, (K // 32, N, S), dtype=torch.int32, device=dev, generator=gen)

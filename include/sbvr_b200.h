@@ -56,6 +56,11 @@ SBVR_API const char* sbvr_strerror(int status);
 
 /* cudaError_t of the last failed runtime call made by this library on the calling thread. */
 SBVR_API int sbvr_last_cuda_error(void);
+/* Which wait ran out, as recorded by the kernel, for the last SBVR_ERR_TIMEOUT that sbvr_workspace_status returned in this
+ * process (0 if none): 0x3xx decode GEMV, 0x4xx small-batch kernel, 0x7xx all-reduce kernels, others the GEMM. */
+SBVR_API unsigned int sbvr_last_timeout_where(void);
+/* Two more words of that record where the kernel leaves them (small-batch kernel: N, and K / 256 << 16 | M << 8 | CTA). */
+SBVR_API unsigned int sbvr_last_timeout_info(int i);
 
 /* Device facts the launch heuristics use.  Replaces `_sbvr_cuda_init` (sbvr/kernels/sbvr_ops.cpp:122-150,
  * bound at :153), which cached cudaDeviceProp for every device and printed them.  Any out pointer may be NULL. */
@@ -100,8 +105,8 @@ SBVR_API int sbvr_decode_f16(const uint32_t* bvr, const void* coeff_idx, int idx
  *       N a multiple of 128; needs a workspace of sbvr_workspace_bytes(...));
  *   4 = tcgen05 FP4 tensor-core kernel for small batches (2 <= M <= 32, at most 16 for G = 128; S, G, N and alignment as
  *       for algo 2, K a multiple of 256 and at most 32768; the activations are quantised by a small kernel in front;
- *       needs a workspace of sbvr_workspace_bytes(...)).  Picked by algo 0 for 5 <= M <= 16 on weights large enough
- *       to give every SM eight (three-tile group, 256-k block) steps. */
+ *       needs a workspace of sbvr_workspace_bytes(...)).  Never picked by algo 0 (see the note at the dispatch in
+ *       csrc/api.cu): on request only. */
 SBVR_API int sbvr_linear_f16(const void* x, const uint32_t* bvr, const void* coeff_idx, int idx_bytes, const void* coeff,
                     int C, const void* bias, void* y, int M, int N, int K, int S, int G, int algo,
                     sbvr_workspace_t* ws, sbvr_stream_t stream);

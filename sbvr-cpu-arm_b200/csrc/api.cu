@@ -77,6 +77,9 @@ const char* sbvr_strerror(int status) {
 }
 
 int sbvr_last_cuda_error(void) { return g_last_cuda_error; }
+static unsigned int g_last_timeout_where = 0, g_last_timeout_info[2] = {0, 0};
+unsigned int sbvr_last_timeout_where(void) { return g_last_timeout_where; }
+unsigned int sbvr_last_timeout_info(int i) { return (i == 0 || i == 1) ? g_last_timeout_info[i] : 0u; }
 
 int sbvr_query(int device, int* sm_count, int* smem_per_block_optin, int* l2_bytes, int* cc_major, int* cc_minor) {
     DeviceInfo d;
@@ -167,6 +170,8 @@ int sbvr_workspace_status(sbvr_workspace_t* ws, sbvr_stream_t stream) {
     SBVR_CUDA_TRY(cudaMemcpyAsync(h, ws->status, 16, cudaMemcpyDeviceToHost, st));
     SBVR_CUDA_TRY(cudaStreamSynchronize(st));
     if (h[0] != 0) {
+        g_last_timeout_where = h[1];
+        g_last_timeout_info[0] = h[2], g_last_timeout_info[1] = h[3];
         // a kernel gave up: its arrival counters may be half-way; clear everything for the next call
         SBVR_CUDA_TRY(cudaMemsetAsync(ws->base, 0, SBVR_WS_FIXED_BYTES, st));
         SBVR_CUDA_TRY(cudaStreamSynchronize(st));
@@ -204,11 +209,10 @@ int sbvr_linear_f16(const void* x, const uint32_t* bvr, const void* coeff_idx, i
         if (ws && device_info(ws->device, &di) == SBVR_OK && di.cc_major == 10) {
             if (linear_tcs_supported(w, M) && !(reinterpret_cast<uintptr_t>(x) & 15) &&
                 linear_tcs_workspace_bytes(w, M, di.sm_count) <= ws->dyn_bytes) algo = 2;
-            // up to 16 rows on weights large enough to give every SM eight (tile group, k block) steps: measured faster
-            // than the fp16 GEMM there (26.3 against 34.3 us at 14336 x 4096, M = 16), slower on small weights
-            else if (M <= 16 && linear_tcb_supported(w, M) &&
-                     (size_t)(w.N / (w.S == 2 ? 64 : 32) / 3) * (size_t)(w.K / 256) >= (size_t)8 * di.sm_count &&
-                     linear_tcb_workspace_bytes(w, M, di.sm_count) <= ws->dyn_bytes) algo = 4;
+            // The small-batch FP4 kernel (algo 4) is measured faster than the GEMM for up to 16 rows on large weights (26.3
+            // against 34.3 us at 14336 x 4096, M = 16), but is not picked automatically: in the 70B batch-16 decode of the
+            // benchmark one of its bounded waits ran out in two of five runs (compute warps waiting for a digit stage), and the
+            // cause has not been found.  It stays available on request.
             else if (linear_gemm_supported(w, M) &&
                      linear_gemm_workspace_bytes(w, M, di.sm_count) <= ws->dyn_bytes) algo = 3;
         }

@@ -645,6 +645,10 @@ __global__ void __launch_bounds__(tb_threads(NSUB), 1)
         }
     }
     // ------------------------------ teardown ------------------------------
+    if (threadIdx.x == 0 && *abort_flag) {         // which problem gave up: N, and K / 256 | M | CTA (for the host's message)
+        atomicExch(p.status + 2, (unsigned int)p.N);
+        atomicExch(p.status + 3, ((unsigned int)KB << 16) | ((unsigned int)M << 8) | (blockIdx.x & 0xFFu));
+    }
     ts_fence_before();
     __syncthreads();
     ts_fence_after();

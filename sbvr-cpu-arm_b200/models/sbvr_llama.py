@@ -522,4 +522,4 @@ class SBVRLlamaForCausalLM(torch.nn.Module):
         for (dev, st), ws in list(_lib._workspaces.items()):
             rc = ws.status(st)
             if rc != 0:
-                raise RuntimeError("sbvr: " + _lib.strerror(rc))
+                raise RuntimeError("sbvr: " + _lib.strerror(rc) + f" (wait 0x{_lib.lib.sbvr_last_timeout_where():x}, info {_lib.lib.sbvr_last_timeout_info(0)} 0x{_lib.lib.sbvr_last_timeout_info(1):x})")

@@ -26,6 +26,10 @@ lib.sbvr_strerror.argtypes = [_i]
 lib.sbvr_strerror.restype = ctypes.c_char_p
 lib.sbvr_last_cuda_error.argtypes = []
 lib.sbvr_last_cuda_error.restype = _i
+lib.sbvr_last_timeout_where.argtypes = []
+lib.sbvr_last_timeout_where.restype = ctypes.c_uint
+lib.sbvr_last_timeout_info.argtypes = [_i]
+lib.sbvr_last_timeout_info.restype = ctypes.c_uint
 lib.sbvr_query.argtypes = [_i, _ip, _ip, _ip, _ip, _ip]
 lib.sbvr_query.restype = _i
 lib.sbvr_workspace_create.argtypes = [ctypes.POINTER(_vp), _i, _sz]
@@ -86,7 +90,7 @@ lib.sbvr_allreduce_add_rmsnorm_digits_f16.argtypes = [_vp, _vp, _vp, _i, _i, _i,
 lib.sbvr_allreduce_add_rmsnorm_digits_f16.restype = _i
 
 EXPORTS = ["sbvr_popc_mm_f16", "sbvr_linear_t_f16", "sbvr_encode_mse_f16", "sbvr_encode_select_f16", "sbvr_encode_pack", "sbvr_rope_attention_f16", "sbvr_linear_fused_f16", "sbvr_allreduce_add_rmsnorm_f16", "sbvr_linear_push_f16", "sbvr_ll_reduce_add_rmsnorm_f16", "sbvr_ll_reduce_add_rmsnorm_digits_f16", "sbvr_allreduce_add_rmsnorm_digits_f16", "sbvr_add_rmsnorm_f16", "sbvr_rope_append_f16", "sbvr_attention_f16", "sbvr_silu_mul_f16",
-           "sbvr_embedding_f16", "sbvr_argmax_f16", "sbvr_linear_f16_noalloc", "sbvr_workspace_bytes", "sbvr_strerror", "sbvr_last_cuda_error", "sbvr_query", "sbvr_workspace_create",
+           "sbvr_embedding_f16", "sbvr_argmax_f16", "sbvr_linear_f16_noalloc", "sbvr_workspace_bytes", "sbvr_strerror", "sbvr_last_cuda_error", "sbvr_last_timeout_where", "sbvr_last_timeout_info", "sbvr_query", "sbvr_workspace_create",
            "sbvr_workspace_destroy", "sbvr_workspace_status", "sbvr_decode_f16", "sbvr_linear_f16",
            "sbvr_linear_f16_host"]
 
