@@ -47,6 +47,7 @@ constexpr int TB_SF_BYTES = 512;                // 32 rows x 16 B of B scale fac
 constexpr int TB_CW0 = 4;                       // first compute warp
 constexpr int TB_ASTAGE = TS_STAGE_WORDS + 512; // packed words of a 256-k block of one tile + its coefficient data
 constexpr int TB_MAX_BSTAGES = 8;
+constexpr int TB_HDR = 2048;                    // barriers, the contributor list of a shared tile group, flags, tensor-memory base
 __host__ __device__ constexpr int tb_nwg(int NSUB) { return NSUB == 2 ? 2 : 3; }
 __host__ __device__ constexpr int tb_threads(int NSUB) { return (TB_CW0 + 4 * tb_nwg(NSUB)) * 32; }
 __host__ __device__ constexpr int tb_bstage(int NJ) { return NJ * 4096 + TB_SF_BYTES; }
@@ -174,14 +175,16 @@ __global__ void __launch_bounds__(tb_threads(NSUB), 1)
     uint64_t* a_full = reinterpret_cast<uint64_t*>(smem);                            // [NWG][TS_MAX_STAGES]
     uint64_t* mma_bar = a_full + NWG * TS_MAX_STAGES;                                // [NWG][2]
     uint64_t* b_full = mma_bar + 2 * NWG;                                            // [TB_MAX_BSTAGES]
-    uint64_t* b_empty = b_full + TB_MAX_BSTAGES;                                     // [TB_MAX_BSTAGES], NWG arrivals
-    uint64_t* cache_bar = b_empty + TB_MAX_BSTAGES;
+    // [NWG][TB_MAX_BSTAGES]: one barrier per warpgroup and stage, so that every barrier has a single arriving commit (three
+    // issuers' tcgen05.commit on one barrier of count three is the one construct this kernel did not share with the decode GEMV)
+    uint64_t* b_empty = b_full + TB_MAX_BSTAGES;
+    uint64_t* cache_bar = b_empty + NWG * TB_MAX_BSTAGES;
     uint64_t* tmem_ready = cache_bar + 1;
     uint64_t* sf_ready = tmem_ready + 1;
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + TS_HDR - 64);
-    volatile int* done_cnt = reinterpret_cast<volatile int*>(smem + TS_HDR - 48);     // [2] compute warps done with a shared tile group
-    volatile int* ctab = reinterpret_cast<volatile int*>(smem + 448);                 // [128] who contributed to a shared tile group
-    uint32_t* tmem_base_s = reinterpret_cast<uint32_t*>(smem + TS_HDR - 16);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + TB_HDR - 64);
+    volatile int* done_cnt = reinterpret_cast<volatile int*>(smem + TB_HDR - 48);     // [2] compute warps done with a shared tile group
+    volatile int* ctab = reinterpret_cast<volatile int*>(smem + 1024);                 // [128] who contributed to a shared tile group
+    uint32_t* tmem_base_s = reinterpret_cast<uint32_t*>(smem + TB_HDR - 16);
 
     const int KB = p.KB, N = p.N, M = p.M;
     __half* cache_s = reinterpret_cast<__half*>(smem + p.off_cache);
@@ -196,11 +199,10 @@ __global__ void __launch_bounds__(tb_threads(NSUB), 1)
 
     {
         constexpr int NB_A = NWG * TS_MAX_STAGES, NB_M = 2 * NWG;
-        constexpr int NB = NB_A + NB_M + 2 * TB_MAX_BSTAGES + 3;
+        constexpr int NB = NB_A + NB_M + (1 + NWG) * TB_MAX_BSTAGES + 3;
         const int i = threadIdx.x;
         if (i < NB) {
             uint32_t count = 1u;
-            if (i >= NB_A + NB_M + TB_MAX_BSTAGES && i < NB_A + NB_M + 2 * TB_MAX_BSTAGES) count = (uint32_t)NWG;    // b_empty
             if (i == NB - 1) count = 4u;                                                                           // sf_ready
             mbar_init(&a_full[i], count);
             if (i == 0) {
@@ -235,7 +237,11 @@ __global__ void __launch_bounds__(tb_threads(NSUB), 1)
         for (int i = 0; i < n_steps; ++i) {
             const int slot = i % BST;
             // the slot's previous occupant (step i - BST) has been multiplied by every warpgroup
-            if (i >= BST) ts_wait(smem_u32(&b_empty[slot]), (uint32_t)((i / BST - 1) & 1), abort_flag, p.status, 0x410u);
+            if (i >= BST) {
+#pragma unroll
+                for (int wq = 0; wq < NWG; ++wq)
+                    ts_wait(smem_u32(&b_empty[wq * TB_MAX_BSTAGES + slot]), (uint32_t)((i / BST - 1) & 1), abort_flag, p.status, 0x410u);
+            }
             if (lane == 0) {
                 mbar_arrive_expect_tx(&b_full[slot], (uint32_t)BSTAGE);
                 bulk_g2s(bring + (size_t)slot * BSTAGE, p.xb + (size_t)pc.k * BSTAGE, (uint32_t)BSTAGE, &b_full[slot]);
@@ -326,7 +332,7 @@ __global__ void __launch_bounds__(tb_threads(NSUB), 1)
                 asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mbar0 + buf * 8)
                              : "memory");
                 asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
-                                 smem_u32(&b_empty[bslot]))
+                                 smem_u32(&b_empty[w * TB_MAX_BSTAGES + bslot]))
                              : "memory");
             }
             __syncwarp();
@@ -680,7 +686,7 @@ static int tb_plan(const PackedW& w, int M, const DeviceInfo& di, TbPlan* pl) {
     pl->part_bytes = (size_t)pl->grid * 2 * pl->NWG * MP * TN * 4;
     const int cache_bytes = w.idx_bytes ? ts_round_up(w.C * w.S * 2, 16) : 0;
     auto layout = [&](int cb, int ast, int bst) {
-        pl->off_cache = TS_HDR;
+        pl->off_cache = TB_HDR;
         pl->off_aring = ts_round_up(pl->off_cache + cb, 128);
         pl->off_bring = ts_round_up(pl->off_aring + pl->NWG * ast * TB_ASTAGE, 128);
         return pl->off_bring + bst * tb_bstage(pl->NJ);
