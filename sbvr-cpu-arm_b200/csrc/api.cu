@@ -219,10 +219,10 @@ int sbvr_linear_f16(const void* x, const uint32_t* bvr, const void* coeff_idx, i
                 linear_tcs_workspace_bytes(w, M, di.sm_count) <= ws->dyn_bytes) algo = 2;
             // The small-batch FP4 kernel (algo 4) is measured faster than the GEMM for up to 16 rows on large weights (26.3
             // against 34.3 us at 14336 x 4096, M = 16), but is not picked automatically: in the 70B batch-16 decode of the
-            // benchmark one of its bounded waits ran out in two of five runs (compute warps waiting for a digit stage), and the
+            // benchmark one of its bounded waits ran out in three of eleven runs (compute warps waiting for a digit stage), and the
             // cause has not been found.  (The kernel has since been given one release barrier per warpgroup and stage instead of
             // one barrier with three arriving commits; two runs of the benchmark with the automatic choice on then passed,
-            // which against a failure rate of about two in five proves little.)  It stays available on request, and
+            // which against a failure rate of about one in four proves little.)  It stays available on request, and
             // SBVR_AUTO_SMALL_BATCH=1 in the environment puts it back into this choice (for weights that give every SM at
             // least eight steps).
             else if (auto_small_batch() && M <= 16 && linear_tcb_supported(w, M) &&
